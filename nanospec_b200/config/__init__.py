@@ -1,0 +1,10 @@
+from .llama import ConfigError, Llama3RopeScaling, LlamaConfig, read_config_files
+from .recipe import LayerSpec, ModelRecipe, PartSpec, Run
+from .registry import Architecture, register_architecture, registered_architectures, resolve_architecture
+from .engine import EngineConfig
+
+__all__ = [
+    "Architecture", "ConfigError", "EngineConfig", "LayerSpec", "Llama3RopeScaling", "LlamaConfig",
+    "ModelRecipe", "PartSpec", "Run", "read_config_files", "register_architecture",
+    "registered_architectures", "resolve_architecture",
+]

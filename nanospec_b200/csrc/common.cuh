@@ -1,0 +1,89 @@
+// Shared helpers of the sm_100a kernels: element types, error reporting, warp and block
+// reductions.  Every exported function returns 0 on success and a non-zero code otherwise;
+// ns_last_error() gives the text of the last failure on the calling thread.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define NS_API extern "C" __attribute__((visibility("default")))
+
+enum NsDtype { NS_F32 = 0, NS_BF16 = 1 };
+
+enum NsStatus {
+    NS_OK = 0,
+    NS_ERR_UNSUPPORTED = 1,  // a size or option that this kernel refuses
+    NS_ERR_CUDA = 2,         // a CUDA call failed
+    NS_ERR_ARGUMENT = 3,     // inconsistent arguments
+};
+
+// set by ns_fail(), read through ns_last_error()
+extern thread_local char ns_error_text[512];
+
+#define NS_FAIL(code, ...)                                        \
+    do {                                                          \
+        snprintf(ns_error_text, sizeof(ns_error_text), __VA_ARGS__); \
+        return (code);                                            \
+    } while (0)
+
+#define NS_CHECK_LAUNCH(name)                                                             \
+    do {                                                                                  \
+        cudaError_t e_ = cudaGetLastError();                                              \
+        if (e_ != cudaSuccess) NS_FAIL(NS_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+#define NS_CUDA(call)                                                                       \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess) NS_FAIL(NS_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---- element access: everything is computed in float -----------------------------------
+__device__ __forceinline__ float ns_ld(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ns_ld(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void ns_st(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void ns_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float ns_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float ns_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum in a fixed order (warp tree, then warp 0 over the warp partials), so the
+// result does not depend on anything but the block size.  `scratch` holds 32 floats.
+__device__ __forceinline__ float ns_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = ns_warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nwarp) ? scratch[threadIdx.x] : 0.f;
+    if (warp == 0) {
+        t = ns_warp_sum(t);
+        if (lane == 0) scratch[0] = t;
+    }
+    __syncthreads();
+    return scratch[0];
+}
+__device__ __forceinline__ float ns_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = ns_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nwarp) ? scratch[threadIdx.x] : -INFINITY;
+    if (warp == 0) {
+        t = ns_warp_max(t);
+        if (lane == 0) scratch[0] = t;
+    }
+    __syncthreads();
+    return scratch[0];
+}

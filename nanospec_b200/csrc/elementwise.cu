@@ -1,0 +1,175 @@
+// Embedding gather, RMSNorm with the residual sum fused in, and the SwiGLU gate.
+//
+// The residual stream is float in every precision mode: the sum of branch outputs is kept
+// in 32-bit and only the normalised activations that feed a matrix product are rounded to
+// the compute type.
+#include "common.cuh"
+
+thread_local char ns_error_text[512] = "";
+NS_API const char* ns_last_error() { return ns_error_text; }
+
+// ---------------------------------------------------------------------------------------
+// embedding: out[n, :] = float(table[ids[n], :]); a negative id (padding row) gives zeros
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int hidden, int vocab) {
+    const int n = blockIdx.x;
+    const int id = ids[n];
+    float* o = out + (size_t)n * hidden;
+    if (id < 0 || id >= vocab) {
+        for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = ns_ld(row, h);
+}
+
+NS_API int ns_embed(const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab, int dtype,
+                    cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
+    if (dtype == NS_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    else if (dtype == NS_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_embed: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_embed");
+    return NS_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm over the residual stream, with the pending branch output added first:
+//   r = resid[row] + branch[row]        (branch may be absent)
+//   resid[row] = r                      (when write_resid)
+//   out[j]  = r * rsqrt(mean(r^2) + eps) * gain          all in float, rounded once to T
+// `rows` (optional) selects the input rows: output row j reads input row rows[j]; then the
+// residual is not written back (used for the final norm at the wanted positions).
+// ---------------------------------------------------------------------------------------
+template <typename T, int THREADS, int PER_THREAD>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
+                   T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+    __shared__ float scratch[32];
+    const int j = blockIdx.x;
+    const int row = rows ? rows[j] : j;
+    float* r = resid + (size_t)row * hidden;
+    const T* b = branch ? branch + (size_t)row * hidden : nullptr;
+    T* o = out + (size_t)j * hidden;
+
+    float v[PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int h = threadIdx.x + i * THREADS;
+        float x = 0.f;
+        if (h < hidden) {
+            x = r[h];
+            if (b) x += ns_ld(b, h);
+            if (write_resid && b) r[h] = x;
+        }
+        v[i] = x;
+        ss += x * x;
+    }
+    // elements beyond PER_THREAD * THREADS (very wide rows) are handled from memory
+    for (int h = threadIdx.x + PER_THREAD * THREADS; h < hidden; h += THREADS) {
+        float x = r[h];
+        if (b) x += ns_ld(b, h);
+        if (write_resid && b) r[h] = x;
+        ss += x * x;
+    }
+    const float total = ns_block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int h = threadIdx.x + i * THREADS;
+        if (h < hidden) ns_st(o, h, v[i] * inv * gain[h]);
+    }
+    for (int h = threadIdx.x + PER_THREAD * THREADS; h < hidden; h += THREADS) {
+        float x = r[h];
+        if (b && !write_resid) x += ns_ld(b, h);
+        ns_st(o, h, x * inv * gain[h]);
+    }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* resid, const void* branch, const float* gain, void* out, const int* rows,
+                              int n_rows, int hidden, float eps, int write_resid, cudaStream_t stream) {
+    const T* b = (const T*)branch;
+    T* o = (T*)out;
+    if (hidden <= 256)
+        add_rmsnorm_kernel<T, 64, 4><<<n_rows, 64, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+    else if (hidden <= 1024)
+        add_rmsnorm_kernel<T, 128, 8><<<n_rows, 128, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+    else if (hidden <= 4096)
+        add_rmsnorm_kernel<T, 512, 8><<<n_rows, 512, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+    else
+        add_rmsnorm_kernel<T, 1024, 8><<<n_rows, 1024, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+    NS_CHECK_LAUNCH("ns_add_rmsnorm");
+    return NS_OK;
+}
+
+NS_API int ns_add_rmsnorm(float* resid, const void* branch, const float* gain, void* out, const int* rows, int n_rows,
+                          int hidden, float eps, int write_resid, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return NS_OK;
+    if (hidden <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_rmsnorm: hidden=%d", hidden);
+    if (rows && write_resid) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_rmsnorm: a row selection cannot write the residual back");
+    if (dtype == NS_F32)
+        return launch_add_rmsnorm<float>(resid, branch, gain, out, rows, n_rows, hidden, eps, write_resid, stream);
+    if (dtype == NS_BF16)
+        return launch_add_rmsnorm<__nv_bfloat16>(resid, branch, gain, out, rows, n_rows, hidden, eps, write_resid, stream);
+    NS_FAIL(NS_ERR_ARGUMENT, "ns_add_rmsnorm: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------------
+// residual sum alone: resid[row] += branch[row]  (used when no norm follows)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ resid, const T* __restrict__ branch, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += ns_ld(branch, i);
+}
+
+NS_API int ns_residual_add(float* resid, const void* branch, int n_rows, int hidden, int dtype, cudaStream_t stream) {
+    const size_t n = (size_t)n_rows * hidden;
+    if (n == 0) return NS_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == NS_F32)
+        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(resid, (const float*)branch, n);
+    else if (dtype == NS_BF16)
+        residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(resid, (const __nv_bfloat16*)branch, n);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_residual_add: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_residual_add");
+    return NS_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU gate on the packed [gate | up] projection:
+//   out[n, j] = silu(gu[n, j]) * gu[n, inter + j],  silu(a) = a / (1 + exp(-a)),  in float
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / inter;
+    const int j = (int)(i - n * inter);
+    const float g = ns_ld(gu, n * 2 * (size_t)inter + j);
+    const float u = ns_ld(gu, n * 2 * (size_t)inter + inter + j);
+    ns_st(out, i, (g / (1.f + expf(-g))) * u);
+}
+
+NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype, cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * inter;
+    if (total == 0) return NS_OK;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == NS_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (dtype == NS_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_swiglu");
+    return NS_OK;
+}

@@ -1,0 +1,196 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+A step may hold portions of prompts beside single decoded tokens, cut anywhere.  It runs
+only the tokens it is given, as one flattened batch, on the cache that earlier steps left:
+one forward pass for everything, where the reference runs one pass for the decoding
+requests and another for the newly admitted prompts (engine/engine.py:226-229).  The batch
+description follows the reference's `AttnMeta.from_rows` (kv/cache.py:113-157) - positions
+per token, a block table per request - except that cache slots are computed on the device
+from the block table instead of being uploaded per token.
+
+`ModelRunner` owns the model, the cache manager with its device storage, and the scratch
+buffers; generation (engine.py) and trace replay (bin/trace_run) both drive this one object.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache import CacheManager, CacheStorage, PoolExhausted
+from ..parts.context import StepContext, Workspace
+from ..parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into
+    `tokens`) whose logits are wanted."""
+
+    req_id: int
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+class _Staging:
+    """Pinned host buffers for the step description, used in turn so that the host never
+    overwrites one that a copy may still be reading."""
+
+    def __init__(self, depth: int = 2) -> None:
+        self.bufs: list[torch.Tensor | None] = [None] * depth
+        self.events: list[torch.cuda.Event | None] = [None] * depth
+        self.turn = 0
+
+    def get(self, n_ints: int) -> tuple[torch.Tensor, int]:
+        i = self.turn
+        self.turn = (self.turn + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < n_ints:
+            buf = torch.empty(max(n_ints, 4096), dtype=torch.int32).pin_memory()
+            self.bufs[i] = buf
+        return buf, i
+
+    def mark(self, i: int) -> None:
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, num_blocks: int, block_size: int, max_requests: int) -> None:
+        if not model.bound:
+            raise RuntimeError("the model has no weights bound")
+        if model.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device; there is no CPU path")
+        self.model = model
+        self.device, self.dtype = model.device, model.dtype
+        needs = model.lane_needs()
+        self.manager = CacheManager(needs, num_blocks, block_size, max_requests)
+        self.storage = CacheStorage(self.manager, needs, self.dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self.block_size = block_size
+        self.max_positions = model.recipe.max_positions
+        self._staging = _Staging()
+        self._meta_dev: torch.Tensor | None = None
+        self.h2d_bytes_last = 0
+
+    # ---- request life -------------------------------------------------------------------
+    def begin(self, req_id: int) -> None:
+        self.manager.begin(req_id)
+
+    def end(self, req_id: int) -> None:
+        self.manager.end(req_id)
+
+    # ---- building the batch ----------------------------------------------------------------
+    def _reserve(self, entries: list[StepEntry]) -> None:
+        done: list[tuple[int, int]] = []
+        try:
+            for e in entries:
+                if not e.tokens:
+                    raise ValueError(f"request {e.req_id} brings no tokens to the step")
+                if self.manager.seq_len[e.req_id] + len(e.tokens) > self.max_positions:
+                    raise ValueError(
+                        f"request {e.req_id} would reach {self.manager.seq_len[e.req_id] + len(e.tokens)} positions; "
+                        f"the model's limit is {self.max_positions}")
+                before = self.manager.seq_len[e.req_id]
+                self.manager.extend(e.req_id, len(e.tokens))
+                done.append((e.req_id, before))
+        except (PoolExhausted, ValueError):
+            for rid, before in reversed(done):
+                self.manager.rollback(rid, before)
+            raise
+
+    def build_context(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor | None, int]:
+        """Reserves pages, lays the step description out in one pinned buffer and copies it
+        to the device once.  Returns (context, wanted rows on the device or None, n wanted)."""
+        ids = [e.req_id for e in entries]
+        if len(set(ids)) != len(ids):
+            raise ValueError("a request may appear once in a step")
+        vocab = self.model.vocab_size
+        for e in entries:
+            for t in e.tokens:
+                if not 0 <= t < vocab:
+                    raise ValueError(f"token id {t} of request {e.req_id} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"request {e.req_id} wants logits at place {w} of {len(e.tokens)} tokens")
+        m = self.manager
+        starts = [m.seq_len[e.req_id] for e in entries]
+        self._reserve(entries)
+
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        N = sum(q_lens)
+        token_ids, positions, token_req, qo_indptr, want_rows = [], [], [], [0], []
+        for b, (e, s) in enumerate(zip(entries, starts)):
+            base = qo_indptr[-1]
+            token_ids.extend(e.tokens)
+            positions.extend(range(s, s + len(e.tokens)))
+            token_req.extend([b] * len(e.tokens))
+            qo_indptr.append(base + len(e.tokens))
+            want_rows.extend(base + w for w in e.want)
+        slots = [m.state_slot(e.req_id) for e in entries]
+        tables, widths = [], []
+        for gi in range(len(m.groups)):
+            rows = [m.table(gi, e.req_id) for e in entries]
+            width = max(1, max(len(r) for r in rows))
+            flat: list[int] = []
+            for r in rows:
+                flat.extend(r)
+                flat.extend([0] * (width - len(r)))
+            tables.append(flat)
+            widths.append(width)
+
+        parts = [token_ids, positions, token_req, qo_indptr, kv_lens, slots, want_rows, *tables]
+        offsets, total = [], 0
+        for p in parts:
+            offsets.append(total)
+            total += len(p) + (-len(p) % 4)  # 16-byte aligned sections
+        host, turn = self._staging.get(total)
+        flat_all: list[int] = []
+        for p in parts:
+            flat_all.extend(p)
+            flat_all.extend([0] * (-len(p) % 4))
+        host[:total] = torch.tensor(flat_all, dtype=torch.int32)
+        if self._meta_dev is None or self._meta_dev.numel() < total:
+            self._meta_dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
+        dev = self._meta_dev
+        dev[:total].copy_(host[:total], non_blocking=True)
+        self._staging.mark(turn)
+        self.h2d_bytes_last = total * 4
+
+        def view(i: int, n: int) -> torch.Tensor:
+            return dev[offsets[i]: offsets[i] + n]
+
+        group_tables = [view(7 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
+        self.storage.zero_state_slots(m.take_fresh_slots())
+        ctx = StepContext(
+            n_tokens=N, n_requests=B,
+            token_ids=view(0, N), positions=view(1, N), token_req=view(2, N), qo_indptr=view(3, B + 1),
+            kv_len=view(4, B), state_slot=view(5, B),
+            q_lens=q_lens, kv_lens=kv_lens,
+            lanes=self.storage.lane_views(group_tables),
+            workspace=self.workspace, dtype=self.dtype, device=self.device,
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+        )
+        n_want = len(want_rows)
+        return ctx, (view(6, n_want) if n_want else None), n_want
+
+    # ---- running ------------------------------------------------------------------------
+    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Runs the step and returns the normed hidden states at the wanted places, in the
+        order of the entries and of their `want` lists ([n_wanted, hidden]), or None."""
+        ctx, want_rows, n_want = self.build_context(entries)
+        hidden = self.model.forward(ctx, want_rows)  # None when nothing is wanted: the blocks still fill the cache
+        for e in entries:
+            self.manager.trim(e.req_id)
+        return hidden
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """run() followed by the head: float32 logits [n_wanted, vocab] (None if nothing is wanted)."""
+        hidden = self.run(entries)
+        return None if hidden is None else self.model.logits(hidden)

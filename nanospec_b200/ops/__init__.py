@@ -1,0 +1,208 @@
+"""Python faces of the CUDA kernels.  Each function checks its tensors (device, dtype,
+layout) and launches on the current CUDA stream; none of them has a CPU or library path
+except `linear` in bfloat16, which may hand a plain matrix product to cuBLAS.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import lib
+from .lib import KernelError
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dt}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operands must live on a CUDA device; there is no CPU path")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _i32(t: torch.Tensor | None, name: str) -> None:
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n] = float(table[ids[n]]); out is the fp32 residual stream [N, hidden]."""
+    _cuda(table, ids, out)
+    _i32(ids, "ids")
+    n, hidden = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed: out must be contiguous float32 and the table contiguous")
+    if table.shape[1] != hidden or ids.numel() != n:
+        raise KernelError(f"embed: table {tuple(table.shape)}, ids {ids.numel()}, out {tuple(out.shape)} do not agree")
+    lib.call("ns_embed", table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, hidden, table.shape[0],
+             dtype_code(table.dtype), _stream())
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, branch: torch.Tensor | None, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None, write_resid: bool = True) -> torch.Tensor:
+    """resid (+= branch); out = rmsnorm(resid) * gain.  With `rows`, output row j reads
+    input row rows[j] and the residual is left unchanged."""
+    _cuda(resid, branch, gain, out, rows)
+    _i32(rows, "rows")
+    hidden = resid.shape[1]
+    n_rows = out.shape[0]
+    if resid.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the residual stream and the gain are float32")
+    if not (resid.is_contiguous() and out.is_contiguous() and gain.is_contiguous()) or out.shape[1] != hidden \
+            or gain.numel() != hidden:
+        raise KernelError("add_rmsnorm: operands must be contiguous and agree on the width")
+    if branch is not None and (branch.dtype != out.dtype or branch.shape != resid.shape or not branch.is_contiguous()):
+        raise KernelError("add_rmsnorm: the branch must match the residual's shape and the output's dtype")
+    if rows is None and n_rows != resid.shape[0]:
+        raise KernelError("add_rmsnorm: out and resid differ in rows")
+    if rows is not None:
+        if rows.numel() != n_rows:
+            raise KernelError("add_rmsnorm: one row index per output row")
+        write_resid = False
+    lib.call("ns_add_rmsnorm", resid.data_ptr(), _ptr(branch), gain.data_ptr(), out.data_ptr(), _ptr(rows), n_rows,
+             hidden, float(eps), int(bool(write_resid)), dtype_code(out.dtype), _stream())
+    return out
+
+
+def residual_add(resid: torch.Tensor, branch: torch.Tensor) -> torch.Tensor:
+    _cuda(resid, branch)
+    if resid.dtype != torch.float32 or resid.shape != branch.shape or not (resid.is_contiguous() and branch.is_contiguous()):
+        raise KernelError("residual_add: float32 residual and a branch of the same shape, both contiguous")
+    lib.call("ns_residual_add", resid.data_ptr(), branch.data_ptr(), resid.shape[0], resid.shape[1],
+             dtype_code(branch.dtype), _stream())
+    return resid
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, j] = silu(gate_up[n, j]) * gate_up[n, I + j]."""
+    _cuda(gate_up, out)
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype or not (gate_up.is_contiguous() and out.is_contiguous()):
+        raise KernelError("swiglu: gate_up must be [N, 2I] and out [N, I], same dtype, contiguous")
+    lib.call("ns_swiglu", gate_up.data_ptr(), out.data_ptr(), n, inter, dtype_code(out.dtype), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T with fp32 accumulation.
+
+    float32: the CUDA-core kernel (true fp32, k-ascending sums, independent of M).
+    bfloat16: a plain matrix product, handed to cuBLAS as the reference hands its
+    `nn.Linear` calls (model/llama.py:175,184,195); `out` may be bfloat16 or float32.
+    """
+    _cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if x.dtype == torch.float32:
+        if w.dtype != torch.float32 or out.dtype != torch.float32:
+            raise KernelError("linear: a float32 product takes float32 weights and output")
+        if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear: operands must be row-major")
+        lib.call("ns_gemm_f32", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+                 out.stride(0), _stream())
+        return out
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported operand types {x.dtype}, {w.dtype}")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise KernelError(f"linear: unsupported output type {out.dtype}")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, nq: int,
+                  nkv: int, head_dim: int, write_kv: bool = True) -> None:
+    """Rotates q and k of the packed [q | k | v] rows in place / into the cache, stores v."""
+    _cuda(qkv, positions, token_req, block_table, inv_freq, k_cache, v_cache)
+    _i32(positions, "positions"), _i32(token_req, "token_req")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * head_dim or not qkv.is_contiguous():
+        raise KernelError("rope_kv_write: qkv must be contiguous [N, (nq + 2 nkv) * head_dim]")
+    if block_table.dtype != torch.int32 or block_table.stride(1) != 1:
+        raise KernelError("rope_kv_write: block_table must be int32 with unit inner stride")
+    if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
+        raise KernelError("rope_kv_write: inv_freq must be contiguous float32")
+    if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("rope_kv_write: cache pages must be contiguous and of the activations' dtype")
+    lib.call("ns_rope_kv_write", qkv.data_ptr(), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), inv_freq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_size, nq, nkv,
+             head_dim, inv_freq.numel(), n, int(bool(write_kv)), dtype_code(qkv.dtype), _stream())
+
+
+def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      token_req: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, nq: int, nkv: int,
+                      head_dim: int, page_size: int, scale: float | None = None, window: int = 0) -> torch.Tensor:
+    """q: [N, >= nq*head_dim] rows (a view into the packed projection is fine, unit inner
+    stride); out: [N, nq*head_dim].  See csrc/attention_generic.cu for the masking rule."""
+    _cuda(q, k_cache, v_cache, block_table, token_req, positions, out)
+    _i32(positions, "positions"), _i32(token_req, "token_req")
+    n = out.shape[0]
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[0] != n or q.dtype != out.dtype:
+        raise KernelError("attention: q and out must be row-major with the same rows and dtype")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise KernelError("attention: the cache must hold the activations' dtype")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    lib.call("ns_attention_generic", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+             block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(), positions.data_ptr(),
+             out.data_ptr(), out.stride(0), n, nq, nkv, head_dim, page_size, float(scale), int(window),
+             dtype_code(q.dtype), _stream())
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                u: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per row of fp32 logits: (token int32, raw log-prob, processed log-prob)."""
+    _cuda(logits, temperature, top_k, top_p, u)
+    _i32(top_k, "top_k")
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample_rows: logits must be float32 rows")
+    for t, name in ((temperature, "temperature"), (top_p, "top_p"), (u, "u")):
+        if t.dtype != torch.float32 or t.numel() != rows or not t.is_contiguous():
+            raise KernelError(f"sample_rows: {name} must be one contiguous float32 per row")
+    token = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lp_raw = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lp_proc = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lib.call("ns_sample_rows", logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
+             top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(), token.data_ptr(), lp_raw.data_ptr(), lp_proc.data_ptr(),
+             _stream())
+    return token, lp_raw, lp_proc
+
+
+def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> None:
+    """Stores k and v of the packed projection at each token's cache slot, unrotated."""
+    none = torch.empty(0, dtype=torch.float32, device=qkv.device)
+    rope_kv_write(qkv, ctx.positions, ctx.token_req, lane.block_table, none, lane.k, lane.v, lane.page_size, nq, nkv,
+                  head_dim, write_kv=True)
+
+
+def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
+              window: int = 0) -> torch.Tensor:
+    """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
+    Chooses the kernel by dtype, sizes and the shape of the step."""
+    return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
+                             head_dim, lane.page_size, scale, window)

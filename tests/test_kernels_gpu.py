@@ -1,0 +1,279 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch statement of the same operation,
+at sizes other than the engine's tiny models use: widths and vocabularies that are no power
+of two, head sizes in steps of 16, odd group counts, scattered pages.  Where random inputs
+would hide a fault the inputs are made so that it shows (one far key that dominates, a
+window's edge, a key on a page boundary)."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from nanospec_b200 import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(100, 77), (4096, 300), (1536, 1000)])
+def test_embed(dtype, hidden, vocab):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, hidden, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (37,), generator=g).to(torch.int32)
+    ids[5] = -1  # a padding row
+    out = torch.full((37, hidden), 7.0, device=DEV)
+    ops().embed(table, ids.to(DEV), out)
+    want = table.float()[ids.clamp(min=0).long().to(DEV)]
+    want[5] = 0
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [64, 100, 1000, 4096, 5000, 9001])
+def test_add_rmsnorm(dtype, hidden):
+    g = torch.Generator().manual_seed(hidden)
+    n = 13
+    resid = torch.randn(n, hidden, generator=g).to(DEV) * 3
+    branch = torch.randn(n, hidden, generator=g).to(dtype).to(DEV)
+    gain = (1 + 0.1 * torch.randn(hidden, generator=g)).to(DEV)
+    eps = 1e-3
+    want_resid = resid + branch.float()
+    want = plain.plain_rmsnorm(want_resid.cpu(), gain.cpu(), eps).to(DEV)
+    r = resid.clone()
+    out = torch.empty(n, hidden, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r, branch, gain, eps, out)
+    assert torch.allclose(r, want_resid, rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+    # without a branch the residual is untouched
+    r2 = resid.clone()
+    ops().add_rmsnorm(r2, None, gain, eps, out)
+    assert torch.equal(r2, resid)
+    torch.testing.assert_close(out.float(), plain.plain_rmsnorm(resid.cpu(), gain.cpu(), eps).to(DEV), **tol(dtype))
+    # row selection: only the asked rows, residual untouched even with a branch
+    rows = torch.tensor([11, 0, 4], dtype=torch.int32, device=DEV)
+    r3 = resid.clone()
+    out3 = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(r3, branch, gain, eps, out3, rows=rows)
+    assert torch.equal(r3, resid)
+    torch.testing.assert_close(out3.float(), want[rows.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_residual_add(dtype):
+    g = torch.Generator().manual_seed(3)
+    n, inter = 9, 352
+    gu = (torch.randn(n, 2 * inter, generator=g) * 4).to(dtype).to(DEV)
+    out = torch.empty(n, inter, dtype=dtype, device=DEV)
+    ops().swiglu(gu, out)
+    f = gu.float()
+    want = torch.nn.functional.silu(f[:, :inter]) * f[:, inter:]
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+    resid = torch.randn(n, inter, generator=g).to(DEV)
+    want_r = resid + out.float()
+    ops().residual_add(resid, out)
+    assert torch.equal(resid, want_r)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (3, 64, 64), (130, 257, 100), (65, 331, 96), (7, 512, 353)])
+def test_gemm_f32_is_true_fp32_and_independent_of_m(M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(DEV)
+    w = torch.randn(N, K, generator=g).to(DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops().linear(x, w, out)
+    want = (x.double() @ w.double().T)
+    err = (out.double() - want).abs().max().item()
+    assert err < 1e-5 * math.sqrt(K) * 4, err  # fp32 rounding only; TF32 would be ~1e-3
+    # each row alone gives the very same bits as the row inside the batch
+    for m in {0, M // 2, M - 1}:
+        one = torch.empty(1, N, device=DEV)
+        ops().linear(x[m:m + 1].contiguous(), w, one)
+        assert torch.equal(one[0], out[m])
+
+
+def paged(k: torch.Tensor, v: torch.Tensor, page: int, n_pages: int, seed: int):
+    """Scatters contiguous k, v [S, nkv, d] over randomly chosen pages; returns the page
+    tensors and the block table row."""
+    S, nkv, d = k.shape
+    g = torch.Generator().manual_seed(seed)
+    nb = -(-S // page)
+    pages = torch.randperm(n_pages, generator=g)[:nb]
+    kc = torch.zeros(n_pages, page, nkv, d, dtype=k.dtype)
+    vc = torch.zeros(n_pages, page, nkv, d, dtype=k.dtype)
+    for b in range(nb):
+        lo, hi = b * page, min(S, (b + 1) * page)
+        kc[pages[b], : hi - lo] = k[lo:hi]
+        vc[pages[b], : hi - lo] = v[lo:hi]
+    return kc, vc, pages.to(torch.int32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,page", [(6, 3, 16, 4), (8, 2, 64, 16), (5, 5, 48, 8), (4, 1, 128, 16)])
+def test_rope_kv_write(dtype, nq, nkv, d, page):
+    g = torch.Generator().manual_seed(d)
+    n_pages = 160
+    scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    inv = plain.plain_inv_freq(d, 500000.0, scaling)
+    # two requests: one continues at a late position (large angles), one starts at 0
+    starts, lens = [301, 0], [7, 12]
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    tables_big = torch.stack([perm[:80], perm[80:]])  # disjoint, scattered pages for every logical block
+    positions, token_req = [], []
+    for r, (s, n) in enumerate(zip(starts, lens)):
+        positions += list(range(s, s + n))
+        token_req += [r] * n
+    positions.insert(3, 0), token_req.insert(3, -1)  # a padding row in the middle
+    N = len(positions)
+    qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    kc = torch.zeros(n_pages, page, nkv, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    dev_qkv = qkv.clone().to(DEV)
+    ops().rope_kv_write(dev_qkv, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                        torch.tensor(token_req, dtype=torch.int32, device=DEV), tables_big.to(DEV), inv.to(DEV), kc, vc,
+                        page, nq, nkv, d)
+    f = qkv.float()
+    pos_t = torch.tensor(positions)
+    q_want = plain.plain_rope(f[:, : nq * d].view(N, nq, d), pos_t, inv)
+    k_want = plain.plain_rope(f[:, nq * d: (nq + nkv) * d].view(N, nkv, d), pos_t, inv)
+    v_in = f[:, (nq + nkv) * d:].view(N, nkv, d)
+    got = dev_qkv.float().cpu()
+    for n in range(N):
+        if token_req[n] < 0:
+            assert torch.equal(got[n], f[n])  # padding rows are left alone
+            continue
+        torch.testing.assert_close(got[n, : nq * d].view(nq, d), q_want[n], **tol(dtype))
+        pg = int(tables_big[token_req[n], positions[n] // page])
+        off = positions[n] % page
+        torch.testing.assert_close(kc[pg, off].float().cpu(), k_want[n], **tol(dtype))
+        assert torch.equal(vc[pg, off].float().cpu(), v_in[n])
+        # v and the unrotated part of the row stay as they were
+        assert torch.equal(got[n, nq * d:], f[n, nq * d:])
+    assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) == sum(lens)  # nothing else was written
+
+
+def attention_case(dtype, nq, nkv, d, page, S, window, spike_key=None, seed=0):
+    """One request of S positions; the last `q_len` are this step's queries."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(S, nq, d, generator=g)
+    k = torch.randn(S, nkv, d, generator=g)
+    v = torch.randn(S, nkv, d, generator=g)
+    if spike_key is not None:
+        # one far key that every query must find: scale it and align the queries with it
+        k[spike_key] = 4.0 * k[spike_key] / k[spike_key].norm(dim=-1, keepdim=True) * math.sqrt(d)
+        q = q + 0.75 * k[spike_key].repeat_interleave(nq // nkv, dim=0)[None]
+        v[spike_key] = 10.0
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    want = plain.plain_attention(q.float(), k.float(), v.float(), window=window)
+    return q, k, v, want
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,page,S,window,spike", [
+    (6, 3, 16, 4, 70, 0, None),
+    (8, 2, 64, 16, 300, 0, 3),       # a far key among hundreds
+    (4, 1, 128, 16, 257, 0, 255),    # the key just before a page edge
+    (12, 4, 80, 8, 150, 0, 64),      # head size in steps of 16, key on a page's first slot
+    (5, 5, 48, 8, 130, 17, 100),     # window whose edge falls inside a page
+    (8, 8, 32, 16, 96, 32, 64),      # window edge on a page edge: key 64 is the first visible to query 95
+    (2, 1, 256, 16, 40, 0, None),
+    (7, 7, 8, 16, 50, 0, 1),
+])
+def test_attention_generic(dtype, nq, nkv, d, page, S, window, spike):
+    q, k, v, want = attention_case(dtype, nq, nkv, d, page, S, window, spike, seed=S)
+    n_pages = 2 * (-(-S // page)) + 3
+    kc, vc, table = paged(k, v, page, n_pages, seed=S + 1)
+    for q_len in (1, 2, S // 3, S):  # decode, a two-token portion, a portion in the middle, the whole
+        start = S - q_len
+        positions = torch.arange(start, S, dtype=torch.int32, device=DEV)
+        token_req = torch.zeros(q_len, dtype=torch.int32, device=DEV)
+        # q sits inside a wider row, as in the packed projection
+        qrow = torch.zeros(q_len, (nq + 2 * nkv) * d, dtype=dtype)
+        qrow[:, : nq * d] = q[start:].reshape(q_len, nq * d)
+        out = torch.empty(q_len, nq * d, dtype=dtype, device=DEV)
+        ops().attention_generic(qrow.to(DEV), kc.to(DEV), vc.to(DEV), table[None].to(DEV), token_req, positions, out,
+                                nq, nkv, d, page, None, window)
+        torch.testing.assert_close(out.float().cpu().view(q_len, nq, d), want[start:],
+                                   **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)))
+
+
+def test_attention_generic_batch_of_requests_and_padding():
+    dtype = torch.float32
+    nq, nkv, d, page = 4, 2, 32, 8
+    cases = [attention_case(dtype, nq, nkv, d, page, S, 0, spike, seed=S) for S, spike in ((33, 2), (8, None), (100, 50))]
+    n_pages = 64
+    kc = torch.zeros(n_pages, page, nkv, d)
+    vc = torch.zeros_like(kc)
+    tables = torch.zeros(3, 16, dtype=torch.int32)
+    free = list(torch.randperm(n_pages, generator=torch.Generator().manual_seed(5)).tolist())
+    for r, (q, k, v, _) in enumerate(cases):
+        S = k.shape[0]
+        for b in range(-(-S // page)):
+            pg = free.pop()
+            tables[r, b] = pg
+            lo, hi = b * page, min(S, (b + 1) * page)
+            kc[pg, : hi - lo], vc[pg, : hi - lo] = k[lo:hi], v[lo:hi]
+    q_lens = [1, 8, 13]
+    rows, positions, token_req, want = [], [], [], []
+    for r, ((q, k, v, w), n) in enumerate(zip(cases, q_lens)):
+        S = k.shape[0]
+        rows.append(q[S - n:].reshape(n, nq * d))
+        want.append(w[S - n:])
+        positions += list(range(S - n, S))
+        token_req += [r] * n
+    qrows = torch.cat(rows)
+    # a padding row at the end
+    qrows = torch.cat([qrows, torch.zeros(1, nq * d)])
+    positions.append(0), token_req.append(-1)
+    out = torch.full((qrows.shape[0], nq * d), 5.0, device=DEV)
+    ops().attention_generic(qrows.to(DEV), kc.to(DEV), vc.to(DEV), tables.to(DEV),
+                            torch.tensor(token_req, dtype=torch.int32, device=DEV),
+                            torch.tensor(positions, dtype=torch.int32, device=DEV), out, nq, nkv, d, page)
+    torch.testing.assert_close(out[:-1].cpu().view(-1, nq, d), torch.cat(want), rtol=1e-4, atol=1e-5)
+    assert torch.equal(out[-1].cpu(), torch.full((nq * d,), 5.0))  # padding row untouched
+
+
+@pytest.mark.parametrize("vocab", [331, 1000, 128256])
+def test_sample_rows(vocab):
+    g = torch.Generator().manual_seed(vocab)
+    rows = 12
+    z = torch.randn(rows, vocab, generator=g) * 2.5
+    z[0, 17] = z[0, 200] = z[0].max() + 1.0  # a tie for the maximum: the lowest index wins
+    temps = [0.0, 0.0, 0.8, 1.0, 1.3, 0.7, 1.0, 0.5, 1.0, 2.0, 0.9, 1.0]
+    top_k = [0, 0, 0, 0, 5, 0, 7, 50, 1, 0, vocab + 5, 3]
+    top_p = [1.0, 1.0, 1.0, 1.0, 1.0, 0.6, 0.9, 0.95, 1.0, 0.3, 1.0, 0.0]
+    us = torch.rand(rows, generator=g).tolist()
+    us[3] = 0.999999
+    tok, lp_raw, lp_proc = ops().sample_rows(
+        z.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(top_k, dtype=torch.int32, device=DEV),
+        torch.tensor(top_p, device=DEV), torch.tensor(us, device=DEV))
+    tok, lp_raw, lp_proc = tok.cpu().tolist(), lp_raw.cpu(), lp_proc.cpu()
+    lse = z.logsumexp(-1)
+    for r in range(rows):
+        if temps[r] == 0:
+            want = int(z[r].argmax()) if r else 17
+            assert tok[r] == want and lp_proc[r] == 0
+        else:
+            lp = plain.plain_process(z[r], temps[r], top_k[r], top_p[r])
+            want = plain.plain_draw(lp, us[r])
+            if tok[r] != want:
+                # an inverse-CDF draw may flip at a boundary of the cdf under another order of sums
+                cdf = lp.exp().cumsum(-1)
+                target = us[r] * cdf[-1]
+                near = min(abs(float(cdf[min(tok[r], want)] - target)), abs(float(cdf[max(tok[r], want) - 1] - target)))
+                assert abs(tok[r] - want) >= 1 and near < 1e-5, (r, tok[r], want, near)
+            assert torch.isfinite(lp[tok[r]]), f"row {r}: token {tok[r]} lies outside the kept set"
+            assert abs(float(lp_proc[r]) - float(lp[tok[r]])) < 1e-4
+        assert abs(float(lp_raw[r]) - float(z[r, tok[r]] - lse[r])) < 1e-4
