@@ -1,0 +1,209 @@
+"""Command line: `python -m nanospec_b200 <command> ...`.
+
+    generate        run prompts of token ids through the engine, print one JSON line per prompt
+    bench           the reference's harness in this engine's terms (python -m bench.run nanospec
+                    --config nospec --bs 1 8 32 --max-tokens 256 --runs 3 there, bench/run.py:162-177):
+                    one JSON line per (batch size, run) with tok_s and tpot_ms
+    random-weights  write a model folder with seeded random weights from sizes or a config.json
+    replay          trace replay (the same program as bin/trace_run)
+
+The model folder comes from --model or the NANOSPEC_MODEL environment variable, as in the
+reference (bench/run.py:24).  Token ids go in and come out; there is no tokenizer inside.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+
+def _model_arg(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--model", default=os.environ.get("NANOSPEC_MODEL"), help="model folder (or $NANOSPEC_MODEL)")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+
+
+def _engine_args(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--num-blocks", type=int, default=None, help="cache pages (default: sized for the workload)")
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--max-running", type=int, default=None)
+    ap.add_argument("--max-admit", type=int, default=32)
+    ap.add_argument("--max-step-tokens", type=int, default=8192)
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+
+
+def _load(args):
+    import torch
+
+    from .weights import load_model
+
+    if not args.model:
+        sys.exit("no model folder: give --model or set NANOSPEC_MODEL")
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    return load_model(args.model, device="cuda", dtype=dtype)
+
+
+def _engine(model, args, num_blocks: int):
+    from .config import EngineConfig
+    from .engine import Engine
+
+    return Engine(model, EngineConfig(
+        num_blocks=args.num_blocks or num_blocks, block_size=args.block_size, max_admit=args.max_admit,
+        max_running=args.max_running, cuda_graphs=not args.no_cuda_graphs, max_step_tokens=args.max_step_tokens,
+        prefill_chunk=args.prefill_chunk, admission=args.admission))
+
+
+def cmd_generate(args) -> int:
+    import torch
+
+    from .engine import SamplingParams
+
+    model = _load(args)
+    prompts: list[list[int]] = []
+    for p in args.prompt_ids or []:
+        prompts.append([int(t) for t in p.replace(",", " ").split()])
+    if args.prompt_lens:
+        g = torch.Generator().manual_seed(args.seed or 0)
+        for n in args.prompt_lens:
+            prompts.append(torch.randint(0, model.vocab_size, (n,), generator=g).tolist())
+    if not prompts:
+        sys.exit("no prompts: give --prompt-ids '1 2 3' (repeatable) or --prompt-lens N ...")
+    need = sum(-(-(len(p) + args.max_tokens) // args.block_size) for p in prompts) + 1
+    engine = _engine(model, args, need)
+    params = [SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
+                             seed=None if args.seed is None else args.seed + i, ignore_eos=args.ignore_eos)
+              for i in range(len(prompts))]
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        print(json.dumps({"request": i, "prompt_len": len(p), "output_ids": o}), flush=True)
+    n_out = sum(len(o) for o in outs)
+    print(json.dumps({"requests": len(prompts), "out_tokens": n_out, "seconds": round(dt, 4),
+                      "tok_s": round(n_out / dt, 1), "steps": engine.steps}), flush=True)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    import torch
+
+    from .engine import SamplingParams
+
+    model = _load(args)
+    g = torch.Generator().manual_seed(0)
+    base = [torch.randint(0, model.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(args.prompts)]
+    prompts = [p for p in base for _ in range(args.n_samples)]
+    for bs in args.bs:
+        for run in range(args.runs):
+            args.max_running = bs
+            args.max_admit = min(bs, 8)  # the reference admits at most 8 new prompts per step (bench/run.py:79)
+            need = bs * (-(-(args.prompt_len + args.max_tokens) // args.block_size) + 1)
+            engine = _engine(model, args, need)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            reqs = [engine.add(p, SamplingParams(args.max_tokens, temperature=args.temperature, seed=i, ignore_eos=True))
+                    for i, p in enumerate(prompts)]
+            while engine.sched.has_work:
+                engine.step()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            n_out = sum(len(r.out_tokens) for r in reqs)
+            print(json.dumps({
+                "engine": "nanospec_b200", "config": "nospec", "bs": bs, "prompts": len(prompts), "out_tokens": n_out,
+                "tok_s": round(n_out / dt, 1), "tpot_ms": round(1000 * dt / (n_out / bs), 2), "run": run,
+                "temperature": args.temperature, "gpu": torch.cuda.get_device_name(0), "dtype": args.dtype,
+                "steps": engine.steps, "data": "seeded uniform random token ids"}), flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    return 0
+
+
+def cmd_random_weights(args) -> int:
+    from .config import Llama3RopeScaling, LlamaConfig
+    from .weights import write_random_model
+
+    if args.config:
+        cfg = json.loads(open(args.config).read())
+    else:
+        scaling = None
+        if args.rope_scaling:
+            f, lo, hi, orig = args.rope_scaling
+            scaling = Llama3RopeScaling(float(f), float(lo), float(hi), int(orig))
+        cfg = LlamaConfig(
+            vocab_size=args.vocab_size, hidden_size=args.hidden_size, intermediate_size=args.intermediate_size,
+            num_hidden_layers=args.num_hidden_layers, num_attention_heads=args.num_attention_heads,
+            num_key_value_heads=args.num_key_value_heads or args.num_attention_heads,
+            head_dim=args.head_dim or args.hidden_size // args.num_attention_heads, rms_norm_eps=args.rms_norm_eps,
+            rope_theta=args.rope_theta, max_position_embeddings=args.max_position_embeddings, rope_scaling=scaling,
+            tie_word_embeddings=args.tie_word_embeddings)
+    print(write_random_model(args.out, cfg, seed=args.seed))
+    return 0
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m nanospec_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate", help="generate from prompts of token ids")
+    _model_arg(g), _engine_args(g)
+    g.add_argument("--prompt-ids", action="append", help="one prompt as ids separated by spaces or commas (repeatable)")
+    g.add_argument("--prompt-lens", type=int, nargs="+", help="seeded random prompts of these lengths")
+    g.add_argument("--max-tokens", type=int, default=128)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=None)
+    g.add_argument("--ignore-eos", action="store_true")
+    g.set_defaults(fn=cmd_generate)
+
+    b = sub.add_parser("bench", help="throughput over batch sizes, one JSON line per run")
+    _model_arg(b), _engine_args(b)
+    b.add_argument("--bs", type=int, nargs="+", default=[1, 8, 32])
+    b.add_argument("--max-tokens", type=int, default=256)
+    b.add_argument("--runs", type=int, default=3)
+    b.add_argument("--temperature", type=float, default=0.0)
+    b.add_argument("--n-samples", type=int, default=1, help="repeat every prompt this many times")
+    b.add_argument("--prompts", type=int, default=80, help="number of distinct prompts")
+    b.add_argument("--prompt-len", type=int, default=64)
+    b.set_defaults(fn=cmd_bench)
+
+    r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
+    r.add_argument("--out", required=True)
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--config", help="a config.json to take every size from")
+    r.add_argument("--vocab-size", type=int, default=256)
+    r.add_argument("--hidden-size", type=int, default=64)
+    r.add_argument("--intermediate-size", type=int, default=128)
+    r.add_argument("--num-hidden-layers", type=int, default=2)
+    r.add_argument("--num-attention-heads", type=int, default=8)
+    r.add_argument("--num-key-value-heads", type=int, default=None)
+    r.add_argument("--head-dim", type=int, default=None)
+    r.add_argument("--rms-norm-eps", type=float, default=1e-5)
+    r.add_argument("--rope-theta", type=float, default=10000.0)
+    r.add_argument("--rope-scaling", nargs=4, metavar=("FACTOR", "LOW", "HIGH", "ORIGINAL_MAX_POS"),
+                   help="llama3 frequency rescale")
+    r.add_argument("--max-position-embeddings", type=int, default=256)
+    r.add_argument("--tie-word-embeddings", action="store_true")
+    r.set_defaults(fn=cmd_random_weights)
+
+    p = sub.add_parser("replay", help="trace replay; same options as bin/trace_run", add_help=False)
+    p.set_defaults(fn=None)
+
+    if argv is None:
+        argv = sys.argv[1:]
+    if argv and argv[0] == "replay":
+        from .engine.replay import main as replay_main
+
+        return replay_main(argv[1:])
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

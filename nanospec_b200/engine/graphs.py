@@ -1,0 +1,191 @@
+"""CUDA-graph replay of decode-only steps, one graph per batch bucket.
+
+As in the reference (engine/graphs.py:22,109-113,171-210) a step in which every request
+brings exactly one token is padded up to the next bucket of (1, 2, 4, ..., 64) requests and
+replayed from a graph captured once for that bucket.  Differences: the attention kernels
+read sequence lengths and block tables from device memory, so nothing has to be planned on
+the host outside the graph; padding rows carry request index -1 and are skipped by every
+kernel instead of writing to a reserved page; and the head projection and the sampling
+kernel are part of the graph, so one replay goes from token ids to next tokens.
+
+The step description of a bucket lives in one pinned host buffer that is copied to one
+device buffer per step; the graph's kernels hold pointers into that device buffer.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..parts.context import StepContext, Workspace
+from .scheduler import Scheduled
+from .step import ModelRunner, StepEntry
+
+
+def _pad4(n: int) -> int:
+    return n + (-n % 4)
+
+
+class _Bucket:
+    """Static buffers and the captured graph of one batch size."""
+
+    def __init__(self, runner: ModelRunner, size: int, table_width: int, workspace: Workspace, pool) -> None:
+        self.size, self.width = size, table_width
+        m = runner.manager
+        n_groups = len(m.groups)
+        names = ["ids", "positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
+                 "temperature", "top_p", "u"]
+        self.off: dict[str, int] = {}
+        total = 0
+        for nm in names:
+            self.off[nm] = total
+            total += _pad4(size + 1 if nm == "qo_indptr" else size)
+        self.table_off = []
+        for _ in range(n_groups):
+            self.table_off.append(total)
+            total += _pad4(size * table_width)
+        self.total = total
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.host_f32 = self.host.view(torch.float32).numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.row_sig: list[tuple | None] = [None] * size
+        self.copied = torch.cuda.Event()
+        self.out_token = torch.zeros(size, dtype=torch.int32, device=runner.device)
+        self.out_lp = torch.zeros(2, size, dtype=torch.float32, device=runner.device)
+        self.out_host = torch.zeros(3, size, dtype=torch.float32).pin_memory()
+        self.logits = torch.zeros(size, runner.model.vocab_size, dtype=torch.float32, device=runner.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        # fixed parts of the description
+        self.host_np[self.off["qo_indptr"]: self.off["qo_indptr"] + size + 1] = np.arange(size + 1, dtype=np.int32)
+        self.host_np[self.off["want_rows"]: self.off["want_rows"] + size] = np.arange(size, dtype=np.int32)
+        self._fill_padding(0)
+        self.dev.copy_(self.host)
+
+        def view(name: str, n: int, dtype=torch.int32) -> torch.Tensor:
+            t = self.dev[self.off[name]: self.off[name] + n]
+            return t if dtype == torch.int32 else t.view(dtype)
+
+        tables = [self.dev[o: o + size * table_width].view(size, table_width) for o in self.table_off]
+        self.ctx = StepContext(
+            n_tokens=size, n_requests=size,
+            token_ids=view("ids", size), positions=view("positions", size), token_req=view("token_req", size),
+            qo_indptr=view("qo_indptr", size + 1), kv_len=view("kv_len", size), state_slot=view("slots", size),
+            q_lens=[1] * size, kv_lens=[table_width * runner.block_size] * size,
+            lanes=runner.storage.lane_views(tables), workspace=workspace, dtype=runner.dtype, device=runner.device,
+            max_q_len=1, max_kv_len=table_width * runner.block_size,
+        )
+        self.ctx.extras["graph"] = True
+        self.want_rows = view("want_rows", size)
+        self.sampling = (view("temperature", size, torch.float32), view("top_k", size), view("top_p", size, torch.float32),
+                         view("u", size, torch.float32))
+        self._capture(runner, pool)
+
+    def _fill_padding(self, first: int) -> None:
+        o, n = self.off, self.size
+        self.host_np[o["ids"] + first: o["ids"] + n] = -1
+        self.host_np[o["token_req"] + first: o["token_req"] + n] = -1
+        self.host_np[o["positions"] + first: o["positions"] + n] = 0
+        self.host_np[o["kv_len"] + first: o["kv_len"] + n] = 0
+        self.host_np[o["slots"] + first: o["slots"] + n] = 0
+        self.host_np[o["top_k"] + first: o["top_k"] + n] = 0
+        self.host_f32[o["temperature"] + first: o["temperature"] + n] = 0.0
+        self.host_f32[o["top_p"] + first: o["top_p"] + n] = 1.0
+        self.host_f32[o["u"] + first: o["u"] + n] = 0.0
+
+    def _forward(self, runner: ModelRunner) -> None:
+        hidden = runner.model.forward(self.ctx, self.want_rows)
+        z = runner.model.logits(hidden, self.logits)
+        t, k, p, u = self.sampling
+        ops.sample_rows(z, t, k, p, u, out=(self.out_token, self.out_lp[0], self.out_lp[1]))
+
+    def _capture(self, runner: ModelRunner, pool) -> None:
+        # two eager runs on a side stream first (every row is padding, nothing touches the cache),
+        # so that scratch buffers and library workspaces exist before the capture
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._forward(runner)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=pool):
+            self._forward(runner)
+        self.graph = g
+
+
+class DecodeGraphs:
+    def __init__(self, runner: ModelRunner, buckets=(1, 2, 4, 8, 16, 32, 64), record_logits: bool = False) -> None:
+        self.runner = runner
+        self.record_logits = record_logits
+        self.sizes = tuple(sorted(buckets))
+        max_context = min(runner.max_positions, runner.manager.num_blocks * runner.block_size)
+        self.table_width = max(1, -(-max_context // runner.block_size))
+        self.workspace = Workspace(runner.device)  # the graphs' own scratch: never grows after capture
+        self.pool = torch.cuda.graph_pool_handle()
+        self.buckets: dict[int, _Bucket] = {}
+        self.replays = 0
+
+    def bucket_size(self, n: int) -> int | None:
+        return next((b for b in self.sizes if b >= n), None)
+
+    def can_run(self, batch: list[Scheduled]) -> bool:
+        return (all(len(s.tokens) == 1 and s.samples for s in batch) and self.bucket_size(len(batch)) is not None)
+
+    def capture_all(self) -> None:
+        for b in reversed(self.sizes):  # largest first: the shared pool is sized by the biggest
+            self._bucket(b)
+
+    def _bucket(self, size: int) -> _Bucket:
+        if size not in self.buckets:
+            self.buckets[size] = _Bucket(self.runner, size, self.table_width, self.workspace, self.pool)
+        return self.buckets[size]
+
+    def run(self, batch: list[Scheduled], uniforms: list[float]):
+        """Reserves pages, fills the bucket's description, copies it, replays, reads the tokens.
+        Returns (tokens, raw log-probs, processed log-probs, logits rows or None)."""
+        runner = self.runner
+        m = runner.manager
+        B = len(batch)
+        bk = self._bucket(self.bucket_size(B))
+        entries = [StepEntry(s.req.id, s.tokens, [0]) for s in batch]
+        starts = [m.seq_len[e.req_id] for e in entries]
+        runner._reserve(entries)
+        bk.copied.synchronize()  # the previous copy out of the pinned buffer has finished
+        o, hn, hf = bk.off, bk.host_np, bk.host_f32
+        hn[o["ids"]: o["ids"] + B] = [s.tokens[0] for s in batch]
+        hn[o["positions"]: o["positions"] + B] = starts
+        hn[o["token_req"]: o["token_req"] + B] = np.arange(B, dtype=np.int32)
+        hn[o["kv_len"]: o["kv_len"] + B] = [st + 1 for st in starts]
+        hn[o["slots"]: o["slots"] + B] = [m.state_slot(e.req_id) for e in entries]
+        hn[o["top_k"]: o["top_k"] + B] = [s.req.params.top_k for s in batch]
+        hf[o["temperature"]: o["temperature"] + B] = [s.req.params.temperature for s in batch]
+        hf[o["top_p"]: o["top_p"] + B] = [s.req.params.top_p for s in batch]
+        hf[o["u"]: o["u"] + B] = uniforms
+        bk._fill_padding(B)
+        W = bk.width
+        for gi, toff in enumerate(bk.table_off):
+            for r, e in enumerate(entries):
+                pages = m.table(gi, e.req_id)
+                cacheable = len(bk.table_off) == 1 and m.groups[gi].spec.window == 0
+                sig = (e.req_id, batch[r].req.preemptions, len(pages), pages[-1] if pages else -1)
+                if cacheable and bk.row_sig[r] == sig:
+                    continue  # this row already holds this request's table
+                hn[toff + r * W: toff + r * W + len(pages)] = pages
+                bk.row_sig[r] = sig if cacheable else None
+        bk.dev.copy_(bk.host, non_blocking=True)
+        bk.copied.record()
+        runner.h2d_bytes_last = bk.total * 4
+        runner.storage.zero_state_slots(m.take_fresh_slots())
+        bk.graph.replay()
+        self.replays += 1
+        bk.out_host[0, :B].copy_(bk.out_token[:B], non_blocking=True)
+        bk.out_host[1:, :B].copy_(bk.out_lp[:, :B], non_blocking=True)
+        raw = bk.logits[:B].cpu() if self.record_logits else None
+        torch.cuda.current_stream().synchronize()
+        for e in entries:
+            m.trim(e.req_id)
+        tok = [int(x) for x in bk.out_host[0, :B].tolist()]
+        return tok, bk.out_host[1, :B].tolist(), bk.out_host[2, :B].tolist(), raw

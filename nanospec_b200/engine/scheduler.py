@@ -1,0 +1,248 @@
+"""Requests and the scheduler above the step function.  No tensors besides the per-request
+random generator.
+
+Kept from the reference (sched/scheduler.py:17-134): `SamplingParams` and `Request` with its
+states, FIFO admission with head-of-line blocking, at most `max_admit` admissions per step
+and `max_running` live requests, worst-case page reservation so that a running request can
+always grow (`admission="reserve"`), `finish`, and `restart` (back to the head of the queue,
+its cache dropped, emitted tokens kept).
+
+Added: prompts are cut into portions under a token budget (`max_step_tokens` per step,
+`prefill_chunk` per request and step), decoding requests and portions of prompts share one
+step, and an optimistic admission mode in which pages can run out.  What happens then is
+decided here: the newest running request is preempted - its pages and state slot are given
+back, it returns to the head of the queue and is recomputed from its prompt plus the tokens
+it has already emitted - until the older requests fit.  A request that could never fit in
+the pool alone is refused when it is added.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache import CacheManager
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    max_tokens: int = 128
+    temperature: float = 0.0  # 0 = greedy
+    top_k: int = 0            # 0 = off
+    top_p: float = 1.0
+    seed: int | None = None   # per-request generator; None = random
+    logprobs: bool = False    # fill Request.logprobs
+    ignore_eos: bool = False  # keep generating past an end-of-sequence token (benchmarks on random weights)
+
+    def __post_init__(self) -> None:
+        if self.max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
+        if self.temperature < 0 or self.top_k < 0 or not 0.0 <= self.top_p <= 1.0:
+            raise ValueError("temperature and top_k must not be negative, top_p must lie in [0, 1]")
+
+
+@dataclass(slots=True)
+class TokenInfo:
+    token: int
+    logprob: float         # log p(token) under the raw logits at temperature 1
+    sample_logprob: float  # log-prob under the (temperature, top-k, top-p) distribution it was drawn from; 0 when greedy
+
+
+@dataclass
+class Request:
+    id: int
+    prompt_ids: list[int]
+    params: SamplingParams
+    out_tokens: list[int] = field(default_factory=list)
+    state: str = "waiting"  # waiting | running | done
+    committed: int = 0      # cache positions written; tokens()[committed:] are still to be fed
+    preemptions: int = 0
+    gen: torch.Generator = None  # CPU generator seeded per request: draws do not depend on the batch
+    logprobs: list[TokenInfo] = field(default_factory=list)
+    step_logits: list = field(default_factory=list)  # only with EngineConfig.record_logits
+
+    def __post_init__(self) -> None:
+        self.gen = torch.Generator()
+        if self.params.seed is not None:
+            self.gen.manual_seed(self.params.seed)
+        else:
+            self.gen.seed()
+
+    def tokens(self) -> list[int]:
+        return self.prompt_ids + self.out_tokens
+
+    @property
+    def seq_len(self) -> int:
+        return len(self.prompt_ids) + len(self.out_tokens)
+
+    @property
+    def pending(self) -> int:
+        """Tokens not yet run through the model (1 while decoding)."""
+        return self.seq_len - self.committed
+
+    @property
+    def final_len(self) -> int:
+        """Most cache positions this request can ever hold."""
+        return len(self.prompt_ids) + self.params.max_tokens - 1
+
+
+@dataclass
+class Scheduled:
+    """One request's share of the next step."""
+
+    req: Request
+    tokens: list[int]
+    samples: bool  # the portion ends at the request's last known token: its last logits give the next token
+
+
+class RequestTooLarge(ValueError):
+    pass
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_admit: int = 32, max_running: int | None = None,
+                 max_step_tokens: int = 8192, prefill_chunk: int = 2048, admission: str = "reserve") -> None:
+        self.cache = cache
+        self.max_admit, self.max_running = max_admit, max_running
+        self.max_step_tokens, self.prefill_chunk = max_step_tokens, prefill_chunk
+        self.admission = admission
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.preempted_total = 0
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- page arithmetic ------------------------------------------------------------------
+    def _longest_portion(self) -> int:
+        return min(self.prefill_chunk, self.max_step_tokens)
+
+    def _peak(self, req: Request) -> list[int]:
+        return self.cache.peak_pages(req.final_len, self._longest_portion())
+
+    def add(self, req: Request) -> None:
+        assert req.state == "waiting"
+        if not req.prompt_ids:
+            raise ValueError("a request needs at least one prompt token")
+        if any(p > g.pool.num_pages for p, g in zip(self._peak(req), self.cache.groups)):
+            raise RequestTooLarge(
+                f"request {req.id} needs up to {self._peak(req)} pages per cache group for {req.final_len} positions; "
+                f"the pool has {self.cache.num_blocks}")
+        self.waiting.append(req)
+
+    # ---- one step's batch -----------------------------------------------------------------
+    def next_batch(self) -> list[Scheduled]:
+        """Decoding requests first (one token each), then portions of running prompts, then
+        admissions; all under the token budget and the pages that are free."""
+        cache = self.cache
+        budget = self.max_step_tokens
+        planned = [0] * len(cache.groups)  # pages this step's entries will take
+        batch: list[Scheduled] = []
+
+        def fits(req_id: int | None, cur: int, n: int) -> bool:
+            need = cache.need(req_id, cur + n)
+            return all(nd + pl <= fr for nd, pl, fr in zip(need, planned, cache.free_pages()))
+
+        def plan(req: Request, n: int) -> None:
+            nonlocal budget
+            need = cache.need(req.id, req.committed + n)
+            for i, nd in enumerate(need):
+                planned[i] += nd
+            toks = req.tokens()[req.committed: req.committed + n]
+            batch.append(Scheduled(req, toks, samples=(n == req.pending)))
+            budget -= n
+
+        def unplan(victim: Request) -> None:
+            nonlocal budget
+            for k, sch in enumerate(batch):
+                if sch.req is victim:
+                    for gi, nd in enumerate(cache.need(victim.id, victim.committed + len(sch.tokens))):
+                        planned[gi] -= nd
+                    budget += len(sch.tokens)
+                    del batch[k]
+                    return
+
+        # 1. running requests: those that decode first (one token each), then portions of
+        #    prompts, each oldest first; when pages run out the newest running request is preempted
+        preempted = False
+        order = [r for r in self.running if r.pending == 1] + [r for r in self.running if r.pending > 1]
+        for req in order:
+            if req.state != "running":
+                continue  # preempted a moment ago
+            if budget <= 0:
+                break
+            n = min(req.pending, self.prefill_chunk, budget)
+            while not fits(req.id, req.committed, n):
+                if self.admission == "reserve":
+                    raise AssertionError("page reservation was violated")  # cannot happen by construction
+                victim = self.running[-1]
+                if victim is req:
+                    if n > 1:  # the newest request itself: try a shorter portion first
+                        n = max(1, n // 2)
+                        continue
+                    if len(self.running) == 1:
+                        raise AssertionError("a single request does not fit in the pool")  # add() refuses these
+                unplan(victim)
+                self.preempt(victim)
+                preempted = True
+                if victim is req:
+                    n = 0
+                    break
+            if n > 0:
+                plan(req, n)
+
+        # 2. admissions, FIFO with head-of-line blocking
+        admitted = 0
+        headroom = None
+        if preempted:
+            return batch  # no admission in a step that had to give pages back
+        if self.admission == "reserve":
+            free = cache.free_pages()
+            owed = [0] * len(cache.groups)
+            for r in self.running:
+                for gi, (pk, held) in enumerate(zip(self._peak(r), cache.held_pages(r.id))):
+                    owed[gi] += max(0, pk - held)
+            headroom = [f - o for f, o in zip(free, owed)]
+        while (self.waiting and admitted < self.max_admit and budget > 0
+               and (self.max_running is None or len(self.running) < self.max_running)
+               and cache.slots.num_free > 0):
+            req = self.waiting[0]
+            n = min(req.pending, self.prefill_chunk, budget)
+            if self.admission == "reserve":
+                peak = self._peak(req)
+                if any(p > h for p, h in zip(peak, headroom)):
+                    break
+                headroom = [h - p for h, p in zip(headroom, peak)]
+            elif not fits(None, 0, n):
+                break
+            self.waiting.popleft()
+            cache.begin(req.id)
+            req.state = "running"
+            self.running.append(req)
+            plan(req, n)
+            admitted += 1
+        return batch
+
+    # ---- transitions -----------------------------------------------------------------------
+    def finish(self, req: Request) -> None:
+        self.running.remove(req)
+        self.cache.end(req.id)
+        req.state = "done"
+
+    def preempt(self, req: Request) -> None:
+        """Pages ran out: drop the request's cache and put it back at the head of the queue.
+        It is recomputed from its prompt plus the tokens it has emitted, which are kept."""
+        self.restart(req)
+        req.preemptions += 1
+        self.preempted_total += 1
+
+    def restart(self, req: Request) -> None:
+        """Back to the head of the queue with nothing cached (the reference's `restart`,
+        sched/scheduler.py:128-134, used there after a weight swap)."""
+        self.running.remove(req)
+        self.cache.end(req.id)
+        req.state, req.committed = "waiting", 0
+        self.waiting.appendleft(req)

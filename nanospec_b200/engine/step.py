@@ -175,7 +175,7 @@ class ModelRunner:
             q_lens=q_lens, kv_lens=kv_lens,
             lanes=self.storage.lane_views(group_tables),
             workspace=self.workspace, dtype=self.dtype, device=self.device,
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens), state_slots_host=slots,
         )
         n_want = len(want_rows)
         return ctx, (view(6, n_want) if n_want else None), n_want

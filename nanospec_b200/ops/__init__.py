@@ -174,8 +174,10 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-                u: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Per row of fp32 logits: (token int32, raw log-prob, processed log-prob)."""
+                u: torch.Tensor, out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None
+                ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per row of fp32 logits: (token int32, raw log-prob, processed log-prob); `out` gives
+    preallocated result tensors (int32, float32, float32, one entry per row)."""
     _cuda(logits, temperature, top_k, top_p, u)
     _i32(top_k, "top_k")
     rows, vocab = logits.shape
@@ -184,9 +186,15 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     for t, name in ((temperature, "temperature"), (top_p, "top_p"), (u, "u")):
         if t.dtype != torch.float32 or t.numel() != rows or not t.is_contiguous():
             raise KernelError(f"sample_rows: {name} must be one contiguous float32 per row")
-    token = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    lp_raw = torch.empty(rows, dtype=torch.float32, device=logits.device)
-    lp_proc = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    if out is not None:
+        token, lp_raw, lp_proc = out
+        if token.dtype != torch.int32 or lp_raw.dtype != torch.float32 or lp_proc.dtype != torch.float32 \
+                or min(token.numel(), lp_raw.numel(), lp_proc.numel()) < rows:
+            raise KernelError("sample_rows: out must be (int32, float32, float32) with one entry per row")
+    else:
+        token = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        lp_raw = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        lp_proc = torch.empty(rows, dtype=torch.float32, device=logits.device)
     lib.call("ns_sample_rows", logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
              top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(), token.data_ptr(), lp_raw.data_ptr(), lp_proc.data_ptr(),
              _stream())

@@ -73,6 +73,7 @@ class StepContext:
     device: torch.device
     max_q_len: int = 0
     max_kv_len: int = 0
+    state_slots_host: list[int] = field(default_factory=list)  # host copy of state_slot
     extras: dict = field(default_factory=dict)
 
     def buffer(self, name: str, cols: int, dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:

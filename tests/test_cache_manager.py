@@ -1,0 +1,187 @@
+"""The cache manager on the host: no page lost, held twice or freed twice, under fixed and
+random orders of requests; windows give pages back early; exhaustion changes nothing; state
+slots (no GPU).  The behaviours of the reference's allocator tests are kept
+(tests/test_allocator.py there): round trip, rollback of whole pages, exhaustion leaves the
+state intact, churn with a check after every operation, scattered pages."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from nanospec_b200.cache import RELEASED, CacheManager, PagePool, PoolExhausted, SlotPool
+from nanospec_b200.parts import CacheNeed, StateNeed
+
+
+def manager(num_blocks=8, block_size=4, lanes=2, window=0, slots=4):
+    return CacheManager([(CacheNeed(2, 8, window), None)] * lanes, num_blocks, block_size, slots)
+
+
+def test_round_trip_and_page_arithmetic():
+    m = manager()
+    m.begin(0)
+    m.extend(0, 5)
+    assert len(m.table(0, 0)) == 2 and m.table(0, 0) == [0, 1]  # page 0 goes out first
+    m.extend(0, 3)  # exactly two full pages: no new page
+    assert len(m.table(0, 0)) == 2
+    m.extend(0, 1)
+    assert len(m.table(0, 0)) == 3 and m.seq_len[0] == 9
+    m.check()
+    m.end(0)
+    assert m.free_pages() == [8] and not m.live
+    m.check()
+
+
+def test_freed_pages_are_used_again_most_recent_first():
+    m = manager()
+    m.begin(0), m.extend(0, 8)
+    m.begin(1), m.extend(1, 4)
+    first = list(m.table(0, 0))
+    m.end(0)
+    m.begin(2), m.extend(2, 4)
+    assert m.table(0, 2)[0] == first[-1]  # LIFO: the page freed last is handed out first
+    m.check()
+
+
+def test_rollback_frees_only_whole_pages_past_the_tail():
+    m = manager()
+    m.begin(0), m.extend(0, 10)
+    pages = list(m.table(0, 0))
+    m.rollback(0, 9)
+    assert m.table(0, 0) == pages
+    m.rollback(0, 8)
+    assert m.table(0, 0) == pages[:2]
+    m.rollback(0, 1)
+    assert m.table(0, 0) == pages[:1] and m.free_pages() == [7]
+    m.rollback(0, 0)
+    assert m.table(0, 0) == [] and m.free_pages() == [8]
+    m.check()
+
+
+def test_exhaustion_raises_and_leaves_everything_as_it_was():
+    m = manager(num_blocks=4, block_size=2)
+    m.begin(0), m.extend(0, 6)
+    m.begin(1)
+    with pytest.raises(PoolExhausted):
+        m.extend(1, 3)
+    assert m.seq_len[1] == 0 and m.table(0, 1) == [] and m.free_pages() == [1]
+    m.check()
+    m.extend(1, 2)
+    assert not m.can_extend(0, 1) and not m.can_extend(1, 1) and m.can_extend(None, 0)
+    m.check()
+
+
+def test_groups_by_geometry_have_pools_of_their_own():
+    needs = [(CacheNeed(2, 8, 0), None), (CacheNeed(2, 8, 6), None), (CacheNeed(2, 8, 0), None), (CacheNeed(1, 16, 0), None),
+             (None, StateNeed((4,)))]
+    m = CacheManager(needs, num_blocks=10, block_size=4, num_state_slots=3)
+    assert len(m.groups) == 3 and m.lane_group == [0, 1, 0, 2, None] and m.state_lanes == [4]
+    assert m.groups[0].spec.lanes == (0, 2) and m.groups[1].spec.window == 6
+    m.begin(7), m.extend(7, 9)
+    assert m.free_pages() == [7, 7, 7]  # each group took its own three pages
+    m.check()
+
+
+def test_window_gives_pages_back_while_the_request_runs():
+    m = manager(num_blocks=6, block_size=4, lanes=1, window=6)
+    m.begin(0)
+    m.extend(0, 9)   # a prompt portion needs all of its positions during the step
+    assert m.free_pages() == [3]
+    assert m.trim(0) == 1  # next query (position 9) reads 4..9: block 0 is behind the window
+    assert m.table(0, 0)[0] == RELEASED and m.free_pages() == [4]
+    m.check()
+    for _ in range(40):  # decoding far beyond the pool's size works: pages are recycled
+        m.extend(0, 1)
+        m.trim(0)
+        m.check()
+        assert m.held_pages(0)[0] <= 3
+    assert m.seq_len[0] == 49
+    with pytest.raises(AssertionError):
+        m.rollback(0, 3)  # behind released pages
+    m.end(0)
+    assert m.free_pages() == [6]
+    m.check()
+
+
+def test_peak_pages_for_reservation():
+    full = manager(num_blocks=100, block_size=4, lanes=1)
+    assert full.peak_pages(33, 8) == [9]
+    win = manager(num_blocks=100, block_size=4, lanes=1, window=6)
+    assert win.peak_pages(33, 8) == [5]    # window - 1 + portion = 13 positions -> 4 pages, + 1 for alignment
+    assert win.peak_pages(7, 8) == [2]     # never more than the whole sequence needs
+
+
+def test_double_begin_double_end_and_double_free_are_caught():
+    m = manager()
+    m.begin(0)
+    with pytest.raises(AssertionError):
+        m.begin(0)
+    m.extend(0, 4)
+    m.end(0)
+    with pytest.raises(KeyError):
+        m.end(0)
+    p = PagePool(4)
+    got = p.take(2)
+    p.give(got)
+    with pytest.raises(AssertionError):
+        p.give(got[:1])
+    with pytest.raises(AssertionError):
+        p.give([9])
+
+
+def test_state_slots():
+    s = SlotPool(2)
+    assert s.acquire(10) == 0 and s.acquire(11) == 1
+    with pytest.raises(PoolExhausted):
+        s.acquire(12)
+    assert s.release(10) == 0 and s.acquire(12) == 0
+    s.check()
+    m = manager(slots=1)
+    m.begin(0)
+    assert m.take_fresh_slots() == [0] and m.take_fresh_slots() == []
+    with pytest.raises(PoolExhausted):
+        m.begin(1)
+    assert 1 not in m.seq_len
+    m.check()
+
+
+@pytest.mark.parametrize("window", [0, 9])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_orders_keep_every_invariant(seed, window):
+    rng = random.Random(seed)
+    m = CacheManager([(CacheNeed(2, 8, 0), None), (CacheNeed(2, 8, window), None)], num_blocks=64, block_size=4,
+                     num_state_slots=12)
+    live, next_id = [], 0
+    for _ in range(600):
+        op = rng.random()
+        try:
+            if live and op < 0.25:
+                m.end(live.pop(rng.randrange(len(live))))
+            elif live and op < 0.35 and window == 0:
+                r = rng.choice(live)
+                m.rollback(r, rng.randint(0, m.seq_len[r]))
+            elif live and op < 0.75:
+                r = rng.choice(live)
+                m.extend(r, rng.randint(1, 30))
+                m.trim(r)
+            else:
+                m.begin(next_id)
+                live.append(next_id)
+                next_id += 1
+                m.extend(live[-1], rng.randint(1, 60))
+                m.trim(live[-1])
+        except PoolExhausted:
+            if next_id - 1 in m.seq_len and next_id - 1 not in live:
+                m.end(next_id - 1)  # begun but no slot in the live list: cannot happen; keeps the test honest
+        m.check()
+        assert sorted(m.live) == sorted(live)
+    # scattered pages: a fresh request lands on pages that are not one contiguous run
+    for r in live[: len(live) // 2]:
+        m.end(r)
+        live.remove(r)
+    if m.can_extend(None, 32) and m.slots.num_free:
+        m.begin(10_000), m.extend(10_000, 32)
+        t = m.table(0, 10_000)
+        assert any(b != a + 1 for a, b in zip(t, t[1:])), t
+    m.check()

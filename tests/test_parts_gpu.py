@@ -1,0 +1,304 @@
+"""The parts of a layer, each alone against its plain statement, and the generality of their
+assembly: a recipe whose order names a layer twice and lets a run read another run's cache,
+and a toy mixer with state of its own that is defined here, registered, built from a model
+folder and stepped - without a change to the framework's files."""
+
+from __future__ import annotations
+
+import json
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+from conftest import random_ids
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda")
+
+
+class _Shell:
+    """Just enough of a model for ModelRunner to build step contexts for parts under test."""
+
+    bound = True
+    device = DEV
+    vocab_size = 1000
+
+    def __init__(self, dtype, needs, max_positions=512):
+        from types import SimpleNamespace
+        self.dtype = dtype
+        self._needs = needs
+        self.recipe = SimpleNamespace(max_positions=max_positions)
+
+    def lane_needs(self):
+        return self._needs
+
+
+def context(dtype, needs, entries, page=8, num_blocks=64):
+    """entries: list of (req_id, n_tokens); returns (runner, ctx)."""
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    runner = ModelRunner(_Shell(dtype, needs), num_blocks, page, 8)
+    for rid, _ in entries:
+        runner.begin(rid)
+    ctx, _, _ = runner.build_context([StepEntry(rid, [1] * n) for rid, n in entries])
+    return runner, ctx
+
+
+def step_context(runner, entries):
+    from nanospec_b200.engine import StepEntry
+    return runner.build_context([StepEntry(rid, [1] * n) for rid, n in entries])[0]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part_alone(dtype):
+    from nanospec_b200.config import PartSpec
+    from nanospec_b200.parts import build_part
+    norm = build_part("norm", PartSpec("rmsnorm", {"hidden": 200, "eps": 1e-4}), dtype, DEV)
+    assert norm.weight_specs()["weight"].shape == (200,)
+    g = torch.Generator().manual_seed(1)
+    gain = 1 + 0.1 * torch.randn(200, generator=g)
+    norm.bind({"weight": gain.to(DEV)})
+    _, ctx = context(dtype, [], [(0, 7)])
+    resid = torch.randn(7, 200, generator=g).to(DEV)
+    pending = torch.randn(7, 200, generator=g).to(dtype).to(DEV)
+    want_resid = resid + pending.float()
+    out = norm.add_norm(resid, pending, ctx)
+    torch.testing.assert_close(resid, want_resid, rtol=0, atol=0)
+    torch.testing.assert_close(out.float().cpu(), plain.plain_rmsnorm(want_resid.cpu(), gain, 1e-4), **tol(dtype))
+
+
+def test_position_part_alone_matches_the_reference_frequencies():
+    from nanospec_b200.config import PartSpec
+    from nanospec_b200.parts import build_part
+    scaling = {"factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
+    for d, theta, sc in ((128, 500000.0, scaling), (64, 500000.0, scaling), (16, 10000.0, None)):
+        rope = build_part("position", PartSpec("rope", {"head_dim": d, "theta": theta, "scaling": sc}), torch.float32, DEV)
+        assert torch.equal(rope.inv_freq_host, plain.plain_inv_freq(d, theta, sc))  # bit for bit
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,d,hidden,window", [(6, 3, 16, 80, 0), (4, 1, 32, 96, 0), (4, 2, 16, 64, 11)])
+def test_attention_mixer_alone_over_two_steps(dtype, heads, kv_heads, d, hidden, window):
+    """The mixer on its own cache lane: a portion, then the rest, against whole-sequence attention."""
+    from nanospec_b200.config import PartSpec
+    from nanospec_b200.parts import build_part
+    pos = PartSpec("rope", {"head_dim": d, "theta": 10000.0, "scaling": None})
+    spec = PartSpec("gqa_attention", {"hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": d,
+                                      "window": window, "position": pos})
+    mixer = build_part("mixer", spec, dtype, DEV)
+    g = torch.Generator().manual_seed(heads)
+    weights = {n: (torch.randn(s.shape, generator=g) * 0.1).to(dtype) for n, s in mixer.weight_specs().items()}
+    mixer.bind({n: t.to(DEV) for n, t in weights.items()})
+    S, cut = 37, 21
+    x = torch.randn(S, hidden, generator=g).to(dtype)
+    wf = {"p." + n: t.float() for n, t in weights.items()}
+    cfg = {"heads": heads, "kv_heads": kv_heads, "head_dim": d}
+    want = plain.plain_attention_block(x.float(), wf, "p.", cfg, torch.arange(S), plain.plain_inv_freq(d, 10000.0, None), window)
+    runner, ctx = context(dtype, [(mixer.cache_need(), mixer.state_need())], [(0, cut)])
+    assert mixer.cache_need().window == window
+    y1 = mixer.forward(x[:cut].to(DEV).contiguous(), ctx, ctx.lanes[0]).clone()
+    runner.manager.trim(0)
+    ctx = step_context(runner, [(0, S - cut)])
+    y2 = mixer.forward(x[cut:].to(DEV).contiguous(), ctx, ctx.lanes[0])
+    torch.testing.assert_close(torch.cat([y1, y2]).float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part_alone(dtype):
+    from nanospec_b200.config import PartSpec
+    from nanospec_b200.parts import build_part
+    ff = build_part("feed_forward", PartSpec("swiglu", {"hidden": 72, "intermediate": 200}), dtype, DEV)
+    g = torch.Generator().manual_seed(2)
+    weights = {n: (torch.randn(s.shape, generator=g) * 0.1).to(dtype) for n, s in ff.weight_specs().items()}
+    ff.bind({n: t.to(DEV) for n, t in weights.items()})
+    x = torch.randn(9, 72, generator=g).to(dtype)
+    _, ctx = context(dtype, [], [(0, 9)])
+    got = ff.forward(x.to(DEV), ctx)
+    want = plain.plain_mlp(x.float(), {"p." + n: t.float() for n, t in weights.items()}, "p.")
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+
+
+# ---------------------------------------------------------------------------------------
+# the order of layers is data
+# ---------------------------------------------------------------------------------------
+def test_a_layer_named_twice_and_a_run_that_reads_another_runs_cache(tmp_path):
+    import dataclasses
+
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.config import Architecture, LlamaConfig, Run, register_architecture
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.weights import load_model, write_random_model
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        # layer 0, layer 1, layer 0 again on a lane of its own, layer 1 again reading the keys
+        # and values that its first run wrote
+        return dataclasses.replace(r, architecture="TwiceForCausalLM",
+                                   order=(Run(0, 0), Run(1, 1), Run(0, 2), Run(1, 1, writes=False)))
+
+    register_architecture(Architecture("TwiceForCausalLM", "twice-test", LlamaConfig.from_hf, recipe))
+    cfg = LlamaConfig(vocab_size=97, hidden_size=48, intermediate_size=80, num_hidden_layers=2, num_attention_heads=3,
+                      num_key_value_heads=1, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      max_position_embeddings=128)
+    hf = cfg.to_hf()
+    hf["architectures"] = ["TwiceForCausalLM"]
+    write_random_model(tmp_path, hf, seed=4)
+    model = load_model(tmp_path, device="cuda", dtype=torch.float32)
+    assert [n[0].head_dim for n in model.lane_needs()] == [16, 16, 16]
+
+    pcfg, w = plain.read_folder(tmp_path)
+    ids = random_ids(29, 97, seed=8)
+    inv = plain.plain_inv_freq(16, 10000.0, None)
+    positions = torch.arange(len(ids))
+
+    def layer(x, i, kv=None):
+        p = f"model.layers.{i}."
+        h = plain.plain_rmsnorm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+        S = x.shape[0]
+        a = p + "self_attn."
+        q = plain.plain_rope((h @ w[a + "q_proj.weight"].T).view(S, 3, 16), positions, inv)
+        if kv is None:
+            k = plain.plain_rope((h @ w[a + "k_proj.weight"].T).view(S, 1, 16), positions, inv)
+            v = (h @ w[a + "v_proj.weight"].T).view(S, 1, 16)
+        else:
+            k, v = kv
+        x = x + plain.plain_attention(q, k, v).reshape(S, -1) @ w[a + "o_proj.weight"].T
+        x = x + plain.plain_mlp(plain.plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"]), w, p + "mlp.")
+        return x, (k, v)
+
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    x, _ = layer(x, 0)
+    x, kv1 = layer(x, 1)
+    x, _ = layer(x, 0)
+    x, _ = layer(x, 1, kv=kv1)
+    want = plain.plain_rmsnorm(x, w["model.norm.weight"], pcfg["eps"]) @ w["lm_head.weight"].T
+
+    runner = ModelRunner(model, num_blocks=16, block_size=4, max_requests=2)
+    runner.begin(0)
+    got = [runner.step([StepEntry(0, ids[:13], list(range(13)))]), runner.step([StepEntry(0, ids[13:27], list(range(14)))]),
+           runner.step([StepEntry(0, ids[27:28], [0])]), runner.step([StepEntry(0, ids[28:], [0])])]
+    torch.testing.assert_close(torch.cat(got).cpu(), want, rtol=2e-5, atol=2e-6)
+
+
+# ---------------------------------------------------------------------------------------
+# a toy mixer with state of its own
+# ---------------------------------------------------------------------------------------
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    """The toy mixer keeps, per request, the running sum of its inputs and a count (fixed-size
+    state, no pages): y_t = W * mean(x_0..x_t).  It is defined here with plain torch
+    operations, registered under a new name, put into a recipe beside an attention layer,
+    written to and loaded from a model folder, and stepped in different cuts and through
+    `Engine.generate`; requests that end give their state slot back and the next request
+    finds it zeroed."""
+    from nanospec_b200 import Engine, EngineConfig, SamplingParams
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.config import Architecture, LayerSpec, LlamaConfig, PartSpec, register_architecture
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.parts import Part, StateNeed, WeightSpec, register_part
+    from nanospec_b200.weights import load_model, write_random_model
+    import dataclasses
+
+    @register_part("mixer", "toy_running_mean")
+    class RunningMean(Part):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.hidden = spec["hidden"]
+
+        def weight_specs(self):
+            return {"mix.weight": WeightSpec((self.hidden, self.hidden))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        def cache_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed((self.hidden + 1,), torch.float32)
+
+        def forward(self, x, ctx, lane, writes=True):
+            out = ctx.buffer("branch", self.hidden)
+            start = 0
+            for b, n in enumerate(ctx.q_lens):
+                slot = ctx.state_slots_host[b]
+                st = lane.state[slot]
+                xs = x[start:start + n].float()
+                sums = st[: self.hidden] + xs.cumsum(0)
+                counts = st[self.hidden] + torch.arange(1, n + 1, device=x.device)
+                mean = (sums / counts[:, None]).to(x.dtype)
+                out[start:start + n] = mean @ self.w.T
+                st[: self.hidden] = sums[-1]
+                st[self.hidden] = counts[-1]
+                start += n
+            return out
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        toy = dataclasses.replace(r.layers[1], mixer=PartSpec("toy_running_mean", {"hidden": cfg.hidden_size}),
+                                  names={**r.layers[1].names, "mixer": "toy."})
+        return dataclasses.replace(r, architecture="ToyForCausalLM", layers=(r.layers[0], toy))
+
+    register_architecture(Architecture("ToyForCausalLM", "toy-test", LlamaConfig.from_hf, recipe))
+    cfg = LlamaConfig(vocab_size=120, hidden_size=40, intermediate_size=56, num_hidden_layers=2, num_attention_heads=5,
+                      num_key_value_heads=5, head_dim=8, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=96)
+    hf = cfg.to_hf()
+    hf["architectures"] = ["ToyForCausalLM"]
+    write_random_model(tmp_path, hf, seed=6)
+    assert "model.layers.1.toy.mix.weight" in json.dumps(sorted(plain.read_folder(tmp_path)[1]))
+    model = load_model(tmp_path, device="cuda", dtype=torch.float32)
+    needs = model.lane_needs()
+    assert needs[0][0] is not None and needs[0][1] is None and needs[1][0] is None and needs[1][1].shape == (41,)
+
+    pcfg, w = plain.read_folder(tmp_path)
+
+    def plain_logits(ids):
+        positions = torch.arange(len(ids))
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        x = plain.plain_layer(x, w, 0, pcfg, positions, plain.plain_inv_freq(8, 10000.0, None))
+        p = "model.layers.1."
+        h = plain.plain_rmsnorm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+        mean = h.cumsum(0) / torch.arange(1, len(ids) + 1)[:, None]
+        x = x + mean @ w[p + "toy.mix.weight"].T
+        x = x + plain.plain_mlp(plain.plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"]), w, p + "mlp.")
+        return plain.plain_rmsnorm(x, w["model.norm.weight"], pcfg["eps"]) @ w["lm_head.weight"].T
+
+    seqs = {0: random_ids(30, 120, seed=1), 1: random_ids(17, 120, seed=2), 2: random_ids(22, 120, seed=3)}
+    runner = ModelRunner(model, num_blocks=24, block_size=4, max_requests=2)
+    got = {r: [] for r in seqs}
+
+    def run(entries):
+        out = runner.step([StepEntry(r, seqs[r][a:b], list(range(b - a))) for r, a, b in entries])
+        row = 0
+        for r, a, b in entries:
+            got[r].append(out[row: row + b - a].cpu())
+            row += b - a
+
+    runner.begin(0), runner.begin(1)
+    run([(0, 0, 11), (1, 0, 2)])
+    run([(1, 2, 3), (0, 11, 13)])
+    run([(0, 13, 30), (1, 3, 17)])
+    runner.end(1)
+    runner.begin(2)  # takes the slot that request 1 held: it must start from zero state
+    run([(2, 0, 9)])
+    run([(2, 9, 22)])
+    runner.end(0), runner.end(2)
+    runner.manager.check()
+    for r, ids in seqs.items():
+        torch.testing.assert_close(torch.cat(got[r]), plain_logits(ids), rtol=3e-5, atol=3e-6)
+
+    # and through the entry point (no graphs: the toy mixer reads host values)
+    eng = Engine(model, EngineConfig(num_blocks=32, block_size=4, cuda_graphs=False, prefill_chunk=7, max_running=2))
+    prompts = [seqs[0][:9], seqs[1][:4], seqs[2][:12]]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=5))
+    for p, o in zip(prompts, outs):
+        ids = list(p)
+        for t in o:
+            z = plain_logits(ids)[-1]
+            top = z.topk(2).values
+            assert t == int(z.argmax()) or float(top[0] - top[1]) < 1e-5
+            ids.append(t)
