@@ -1,0 +1,272 @@
+"""Decode and prefill throughput at the Llama-3.1-8B shape with random weights, one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 32] [--impl reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at the default batch (8 requests,
+each with 1,024 tokens of context), timed on the device with CUDA events around K decode
+steps after W warm-up steps; `e2e` is the same workload through the Python entry point
+(`Engine.step`), with every step's token ids going from pinned host memory to the device and
+the sampled tokens read back, timed on the host clock.  `prefill` is one step of 2,048 prompt
+tokens; `roofline` sets the decode step's bytes (every weight it uses once plus the cache of
+the live requests) against the measured copy bandwidth; `points` holds decode at batch 1 and
+64.  The weights of every step (16 GB) are larger than L2, so nothing is flushed between
+timed iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Llama-3.1-8B: every size of the benchmark's third configuration
+SHAPE = dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+             num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192)
+ROPE = (8.0, 1.0, 4.0, 8192)
+CONTEXT = 1024        # tokens each request holds when decoding is timed
+PREFILL_TOKENS = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            p = json.load(open(path))
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(p.get(k), (int, float)):
+                    out[k] = float(p[k])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def model_bytes_and_flops(cfg: dict, layers: int, batch: int, context: int) -> dict:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nq + 2 * nkv) * d * H + H * nq * d + 2 * I * H + H * I  # matrix elements
+    weights = layers * per_layer + V * H                                 # + the head
+    norms = (2 * layers + 1) * H
+    kv_per_token = 2 * layers * nkv * d * 2                              # bytes, bf16
+    decode_bytes = 2 * weights + 4 * norms + batch * H * 2 + batch * context * kv_per_token
+    def flops(tokens: int, causal_ctx: int) -> float:
+        gemm = 2.0 * tokens * layers * per_layer
+        attn = 4.0 * layers * nq * d * tokens * (causal_ctx / 2.0)  # q k^T and p v over the causal half
+        return gemm + attn
+    return {"weights": weights, "decode_bytes": decode_bytes,
+            "prefill_flops": flops(PREFILL_TOKENS, PREFILL_TOKENS) + 2.0 * V * H}
+
+
+def build_engine(layers: int, batch: int, num_blocks: int, graphs: bool = True):
+    import torch
+
+    from nanospec_b200 import Engine, EngineConfig, LlamaConfig, random_model
+    from nanospec_b200.config import Llama3RopeScaling
+
+    cfg = LlamaConfig(**{**SHAPE, "num_hidden_layers": layers}, rope_scaling=Llama3RopeScaling(*ROPE))
+    model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16)
+    eng = Engine(model, EngineConfig(num_blocks=num_blocks, block_size=PAGE, max_running=max(batch, 1), max_admit=64,
+                                     cuda_graphs=graphs, max_step_tokens=8192, prefill_chunk=PREFILL_TOKENS))
+    return model, eng
+
+
+def prime(eng, batch: int, context: int, max_tokens: int, seed: int = 0):
+    """Adds `batch` requests of `context` random tokens and runs steps until all of them decode."""
+    import torch
+
+    from nanospec_b200 import SamplingParams
+
+    g = torch.Generator().manual_seed(seed)
+    vocab = eng.model.vocab_size
+    reqs = [eng.add(torch.randint(0, vocab, (context - 1,), generator=g).tolist(),
+                    SamplingParams(max_tokens=max_tokens, ignore_eos=True)) for _ in range(batch)]
+    while any(r.pending > 1 or r.state != "running" for r in reqs):
+        eng.step()
+    return reqs
+
+
+def time_decode(eng, batch: int, steps: int, warmup: int) -> tuple[float, float, dict, int]:
+    """(device ms per step, host seconds for the timed steps, byte counts, kernel launches)."""
+    import torch
+
+    from nanospec_b200.ops import lib
+
+    reqs = prime(eng, batch, CONTEXT, max_tokens=steps + warmup + 8)
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    eng.graphs.timing = []  # (start, end) events around each step's copy-in, replay and copy-out
+    launches0 = lib.launch_count()
+    replays0 = eng.graphs.replays if eng.graphs else 0
+    t0 = time.perf_counter()
+    for i in range(steps):
+        eng.step()          # host ids -> pinned -> device, graph replay, sampled tokens back to the host
+    torch.cuda.synchronize()
+    host_s = time.perf_counter() - t0
+    assert len(eng.graphs.timing) == steps, "a timed step did not go through the decode graph"
+    dev_ms = sum(s.elapsed_time(e) for s, e in eng.graphs.timing) / steps
+    eng.graphs.timing = None
+    launches = lib.launch_count() - launches0
+    if eng.graphs:
+        bucket = eng.graphs.buckets[eng.graphs.bucket_size(batch)]
+        launches += (eng.graphs.replays - replays0) * bucket.kernels
+    io = {"h2d": eng.runner.h2d_bytes_last, "d2h": 3 * 4 * batch}
+    for r in reqs:
+        if r.state == "running":
+            eng.sched.finish(r)
+    return dev_ms, host_s, io, launches
+
+
+def time_prefill(eng, warmup: int, iters: int) -> float:
+    import torch
+
+    from nanospec_b200 import SamplingParams
+
+    g = torch.Generator().manual_seed(123)
+    times = []
+    for i in range(warmup + iters):
+        ids = torch.randint(0, eng.model.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+        req = eng.add(ids, SamplingParams(max_tokens=1, ignore_eos=True))
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step()
+        b.record()
+        torch.cuda.synchronize()
+        assert req.state == "done"
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    pk, pk_src = peaks()
+    layers = args.layers
+    sizes = model_bytes_and_flops(SHAPE, layers, args.batch, CONTEXT)
+    pages_per_req = -(-(CONTEXT + args.steps + args.warmup + 64) // PAGE)
+    num_blocks = max(64 * pages_per_req, -(-PREFILL_TOKENS // PAGE) + 8) + 8
+    model, eng = build_engine(layers, 64, num_blocks)
+    if eng.graphs:
+        for b in (64, args.batch, 1):
+            eng.graphs._bucket(eng.graphs.bucket_size(b))
+    torch.cuda.synchronize()
+
+    clocks = ClockSampler()
+    clocks.start()
+    dev_ms, host_s, io, launches = time_decode(eng, args.batch, args.steps, args.warmup)
+    clock_rec = clocks.stop()
+    value = args.batch * 1000.0 / dev_ms
+    e2e = args.batch * args.steps / host_s
+
+    points = {}
+    for b in (1, 64):
+        ms, _, _, _ = time_decode(eng, b, max(4, args.steps // 2), args.warmup)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+    pre_ms = time_prefill(eng, warmup=max(2, args.warmup // 2), iters=3)
+
+    achieved = sizes["decode_bytes"] / (dev_ms * 1e-3) / 1e9
+    peak_tf = pk["bf16_tflops_sustained"] if pre_ms > 50 else pk["bf16_tflops"]
+    return {
+        "metric": "decode tok/s (Llama-3.1-8B shape, batch 8, 1,024-token context)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform random token ids, random N(0, 0.02) weights",
+        "config": {"model": "Llama-3.1-8B shape", "layers": layers, "layers_of_config": SHAPE["num_hidden_layers"],
+                   "hidden": SHAPE["hidden_size"], "heads": SHAPE["num_attention_heads"],
+                   "kv_heads": SHAPE["num_key_value_heads"], "head_dim": SHAPE["head_dim"],
+                   "intermediate": SHAPE["intermediate_size"], "vocab": SHAPE["vocab_size"], "global_batch": args.batch,
+                   "seq_len": CONTEXT, "max_context": SHAPE["max_position_embeddings"], "page": PAGE,
+                   "parallelism": "single GPU", "cuda_graphs": True, "l2": "inputs larger than L2 (16 GB of weights per step)",
+                   "peaks": pk_src},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": io["h2d"], "d2h_bytes_per_step": io["d2h"]},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                    "frac": round(sizes["prefill_flops"] / (pre_ms * 1e-3) / (peak_tf * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_rec,
+    }
+
+
+def run_reference(args) -> dict:
+    # The offline install of the unmodified reference fails while pip generates its metadata:
+    # its pyproject.toml declares no packages and setuptools refuses the flat layout ("Multiple
+    # top-level packages discovered": rl, kv, spec, model, sched, bench, engine), from the
+    # read-only tree and from a writable copy alike, with and without --no-deps.
+    return {"impl": "reference", "unavailable": "pip install of the unmodified reference fails offline: setuptools "
+            "refuses its flat layout (multiple top-level packages, no package list in pyproject.toml)"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"])
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
+        return 2
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -110,9 +110,13 @@ class _Bucket:
                 self._forward(runner)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..ops import lib
+
         g = torch.cuda.CUDAGraph()
+        before = lib.launch_count()
         with torch.cuda.graph(g, pool=pool):
             self._forward(runner)
+        self.kernels = lib.launch_count() - before  # this framework's kernels in one replay
         self.graph = g
 
 
@@ -127,6 +131,7 @@ class DecodeGraphs:
         self.pool = torch.cuda.graph_pool_handle()
         self.buckets: dict[int, _Bucket] = {}
         self.replays = 0
+        self.timing: list | None = None  # set to a list to collect (start, end) CUDA events of each replay
 
     def bucket_size(self, n: int) -> int | None:
         return next((b for b in self.sizes if b >= n), None)
@@ -175,6 +180,9 @@ class DecodeGraphs:
                     continue  # this row already holds this request's table
                 hn[toff + r * W: toff + r * W + len(pages)] = pages
                 bk.row_sig[r] = sig if cacheable else None
+        if self.timing is not None:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
         bk.dev.copy_(bk.host, non_blocking=True)
         bk.copied.record()
         runner.h2d_bytes_last = bk.total * 4
@@ -184,6 +192,9 @@ class DecodeGraphs:
         bk.out_host[0, :B].copy_(bk.out_token[:B], non_blocking=True)
         bk.out_host[1:, :B].copy_(bk.out_lp[:, :B], non_blocking=True)
         raw = bk.logits[:B].cpu() if self.record_logits else None
+        if self.timing is not None:
+            t1.record()
+            self.timing.append((t0, t1))
         torch.cuda.current_stream().synchronize()
         for e in entries:
             m.trim(e.req_id)

@@ -12,6 +12,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 _lib: ctypes.CDLL | None = None
 _path: str | None = None
+_launches = 0  # kernel launches made through `call` (graph replays are counted by their owner)
 
 
 class KernelError(RuntimeError):
@@ -65,11 +66,17 @@ def library_path() -> str | None:
     return _path
 
 
+def launch_count() -> int:
+    return _launches
+
+
 def call(name: str, *args) -> None:
+    global _launches
     lib = load()
     fn = getattr(lib, name, None)
     if fn is None:
         raise KernelError(f"the native library {_path} has no entry point {name}; rebuild it")
     status = fn(*args)
+    _launches += 1
     if status != 0:
         raise KernelError(f"{name} failed with status {status}: {lib.ns_last_error().decode(errors='replace')}")
