@@ -208,9 +208,86 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
                   head_dim, write_kv=True)
 
 
+TILE_Q = 64          # query rows per block of the prefill kernel
+_TARGET_BLOCKS = 592  # decode attention aims at about four blocks per SM of a B200
+
+
+def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
+                     window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None) -> None:
+    """Split-KV decode attention for the requests that bring one token (csrc/attention_decode.cu).
+    `rows`: int32 device tensor of their token rows, or None when every row of the step is one."""
+    head_tiles = -(-(nq // nkv) // 16)
+    n_splits = max(1, min(16, -(-_TARGET_BLOCKS // (n_rows * nkv * head_tiles))))
+    if max_kv_len is not None:
+        n_splits = max(1, min(n_splits, -(-max_kv_len // 64)))
+    ws = ctx.workspace
+    part_o = ws.get("attn_part_o", n_rows * nq * n_splits, head_dim, torch.float32)
+    part_ml = ws.get("attn_part_ml", n_rows * nq * n_splits, 2, torch.float32)
+    counters = ws.get("attn_counters", n_rows * nkv * head_tiles, 1, torch.int32, zero=True)
+    lib.call("ns_attention_decode", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+             lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
+             ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
+             counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
+             n_splits, _stream())
+
+
+def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
+                      window: int, tiles: torch.Tensor) -> None:
+    """Tensor-core attention for portions of prompts (csrc/attention_prefill.cu).
+    `tiles`: int32 [n, 2] of (request, offset among its tokens of this step)."""
+    lib.call("ns_attention_prefill", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+             lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
+             tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
+             float(scale), int(window), _stream())
+
+
+def _attention_plan(ctx) -> dict:
+    """Once per step: which token rows decode, and the query tiles of the prompt portions."""
+    plan = ctx.extras.get("attention_plan")
+    if plan is not None:
+        return plan
+    if ctx.extras.get("graph"):
+        plan = {"decode_rows": None, "n_decode": ctx.n_tokens, "tiles": None, "max_kv_len": None}
+    else:
+        starts, row = [], 0
+        for n in ctx.q_lens:
+            starts.append(row)
+            row += n
+        decode = [s for s, n in zip(starts, ctx.q_lens) if n == 1]
+        tiles = [(b, off) for b, n in enumerate(ctx.q_lens) if n > 1 for off in range(0, n, TILE_Q)]
+        dev = ctx.device
+        plan = {
+            "n_decode": len(decode),
+            "decode_rows": None if len(decode) == ctx.n_tokens or not decode
+            else torch.tensor(decode, dtype=torch.int32).to(dev, non_blocking=True),
+            "tiles": torch.tensor(tiles, dtype=torch.int32).to(dev, non_blocking=True) if tiles else None,
+            "max_kv_len": max((kv for kv, n in zip(ctx.kv_lens, ctx.q_lens) if n == 1), default=None),
+        }
+    ctx.extras["attention_plan"] = plan
+    return plan
+
+
 def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
               window: int = 0) -> torch.Tensor:
     """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
-    Chooses the kernel by dtype, sizes and the shape of the step."""
-    return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
-                             head_dim, lane.page_size, scale, window)
+
+    bfloat16 with a head size that the tensor-core kernels take: the decode kernel for requests
+    that bring one token, the prefill kernel for the others.  float32, and head sizes those
+    kernels refuse: the exact kernel, one warp per (token, head)."""
+    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64:
+        return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
+                                 head_dim, lane.page_size, scale, window)
+    _cuda(qkv, out, lane.k, lane.v, lane.block_table)
+    if out.stride(1) != 1 or qkv.stride(1) != 1 or lane.k.dtype != qkv.dtype:
+        raise KernelError("attention: row-major bfloat16 operands and a bfloat16 cache are needed")
+    plan = _attention_plan(ctx)
+    if plan["n_decode"]:
+        attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
+                         plan["max_kv_len"])
+    if plan["tiles"] is not None:
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"])
+    return out

@@ -29,14 +29,17 @@ class Workspace:
         self._bufs: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
         self.frozen = False  # set while CUDA graphs hold pointers into the buffers
 
-    def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, rows: int, cols: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """`zero`: the buffer is zero-filled when it is (re)allocated - for scratch that its
+        kernel leaves zeroed after every use."""
         key = (name, cols, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < rows:
             if self.frozen and buf is not None:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while CUDA graphs point into it")
             cap = max(rows, 16 if buf is None else 2 * buf.shape[0])
-            buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make((cap, cols), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:rows]
 

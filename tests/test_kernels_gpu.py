@@ -277,3 +277,76 @@ def test_sample_rows(vocab):
             assert torch.isfinite(lp[tok[r]]), f"row {r}: token {tok[r]} lies outside the kept set"
             assert abs(float(lp_proc[r]) - float(lp[tok[r]])) < 1e-4
         assert abs(float(lp_raw[r]) - float(z[r, tok[r]] - lse[r])) < 1e-4
+
+
+# ---------------------------------------------------------------------------------------
+# the bfloat16 tensor-core attention kernels (decode: split-KV; prefill: 64-query tiles)
+# ---------------------------------------------------------------------------------------
+def _step(requests, nq, nkv, d, page, n_pages, seed):
+    """requests: list of (S, q_len, spike).  Builds one paged cache for all of them and the
+    flattened step; returns (ctx, lane, qkv rows, expected outputs per request)."""
+    from types import SimpleNamespace
+    from nanospec_b200.parts import Workspace
+    kc = torch.zeros(n_pages, page, nkv, d, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    free = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max(-(-S // page) for S, _, _ in requests)
+    tables = torch.zeros(len(requests), width, dtype=torch.int32)
+    rows, positions, token_req, qo, want, windows = [], [], [], [0], [], None
+    for r, (S, q_len, spike) in enumerate(requests):
+        q, k, v, _ = attention_case(torch.bfloat16, nq, nkv, d, page, S, 0, spike, seed=seed + 7 * r)
+        for b in range(-(-S // page)):
+            pg = free.pop()
+            tables[r, b] = pg
+            lo, hi = b * page, min(S, (b + 1) * page)
+            kc[pg, : hi - lo], vc[pg, : hi - lo] = k[lo:hi], v[lo:hi]
+        rows.append(q[S - q_len:].reshape(q_len, nq * d))
+        positions += list(range(S - q_len, S))
+        token_req += [r] * q_len
+        qo.append(qo[-1] + q_len)
+        want.append((q.float(), k.float(), v.float(), S - q_len))
+    N = len(positions)
+    qkv = torch.zeros(N, (nq + 2 * nkv) * d, dtype=torch.bfloat16)
+    qkv[:, : nq * d] = torch.cat(rows)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    ctx = SimpleNamespace(n_tokens=N, token_req=i32(token_req), positions=i32(positions), qo_indptr=i32(qo),
+                          q_lens=[q for _, q, _ in requests], kv_lens=[S for S, _, _ in requests], device=torch.device(DEV),
+                          extras={}, workspace=Workspace(torch.device(DEV)), max_q_len=max(q for _, q, _ in requests))
+    lane = SimpleNamespace(k=kc.to(DEV), v=vc.to(DEV), block_table=tables.to(DEV), page_size=page)
+    return ctx, lane, qkv.to(DEV), want
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (8, 2, 128, 16, 0), (4, 1, 32, 8, 0), (6, 3, 16, 4, 0), (12, 4, 80, 16, 0), (5, 5, 48, 8, 0), (32, 8, 64, 16, 0),
+    (8, 2, 64, 16, 100), (4, 4, 112, 8, 64), (40, 2, 32, 16, 0),
+])
+def test_tensor_core_attention_mixed_step(nq, nkv, d, page, window):
+    """Decode rows beside portions of prompts in one step: (S, q_len, far key that must be found)."""
+    requests = [(700, 1, 3), (65, 1, 64), (130, 130, 5), (333, 70, 2), (64, 2, 63), (1, 1, None), (257, 129, 128), (90, 1, None)]
+    ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=2000 // page + 40, seed=d + nq)
+    out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+    ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), window)
+    assert ctx.extras["attention_plan"]["n_decode"] == 4 and ctx.extras["attention_plan"]["tiles"].shape[0] == 3 + 2 + 1 + 3
+    row = 0
+    for (S, q_len, _), (q, k, v, start) in zip(requests, want):
+        full = plain.plain_attention(q, k, v, window=window)
+        torch.testing.assert_close(out[row: row + q_len].float().cpu().view(q_len, nq, d), full[start:], rtol=3e-2, atol=3e-2)
+        row += q_len
+
+
+@pytest.mark.parametrize("n_req,S", [(1, 1500), (3, 1030), (64, 70)])
+def test_decode_attention_splits_and_counters(n_req, S):
+    """Decode only, long enough that the keys are split over several blocks; run twice on the same
+    scratch (the counters must come back to zero) and in the layout a captured graph uses."""
+    nq, nkv, d, page = 8, 2, 128, 16
+    requests = [(S - 13 * r, 1, (S - 13 * r) // 2) for r in range(n_req)]
+    ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=n_req * (S // page + 2), seed=S)
+    for graph in (False, True):
+        ctx.extras = {"graph": True} if graph else {}
+        for _ in range(2):
+            out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+            ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+            for r, (q, k, v, start) in enumerate(want):
+                full = plain.plain_attention(q, k, v)
+                torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
+        assert int(ctx.workspace.get("attn_counters", 1, 1, torch.int32).sum()) == 0
