@@ -5,6 +5,7 @@
                     --config nospec --bs 1 8 32 --max-tokens 256 --runs 3 there, bench/run.py:162-177):
                     one JSON line per (batch size, run) with tok_s and tpot_ms
     random-weights  write a model folder with seeded random weights from sizes or a config.json
+    profile         one decode or prefill step at a named shape, bracketed for a profiler
     replay          trace replay (the same program as bin/trace_run)
 
 The model folder comes from --model or the NANOSPEC_MODEL environment variable, as in the
@@ -123,6 +124,64 @@ def cmd_bench(args) -> int:
     return 0
 
 
+def cmd_profile(args) -> int:
+    """One decode step or one prefill step at a named shape with random weights, bracketed by
+    cudaProfilerStart/Stop so that a profiler started with --profile-from-start off sees only it."""
+    import torch
+
+    from .config import Llama3RopeScaling, LlamaConfig
+    from .engine import SamplingParams
+    from .weights import random_model
+
+    shapes = {
+        "8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
+                   num_key_value_heads=8, head_dim=128, layers=32, factor=8.0),
+        "3b": dict(vocab_size=128256, hidden_size=3072, intermediate_size=8192, num_attention_heads=24,
+                   num_key_value_heads=8, head_dim=128, layers=28, factor=32.0),
+        "1b": dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
+                   num_key_value_heads=8, head_dim=64, layers=16, factor=32.0),
+    }
+    sh = dict(shapes[args.shape])
+    layers = args.layers or sh.pop("layers")
+    sh.pop("layers", None)
+    factor = sh.pop("factor")
+    cfg = LlamaConfig(**sh, num_hidden_layers=layers, rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
+                      rope_scaling=Llama3RopeScaling(factor, 1.0, 4.0, 8192))
+    model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
+    args.max_running = max(args.batch, 1)
+    args.max_admit = 64
+    pages = args.batch * (-(-(args.context + 64) // args.block_size) + 1) + 8
+    engine = _engine(model, args, pages)
+    g = torch.Generator().manual_seed(0)
+    n_prompt = args.context - 1 if args.what == "decode" else args.context
+    reqs = [engine.add(torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist(),
+                       SamplingParams(max_tokens=32 if args.what == "decode" else 1, ignore_eos=True)) for _ in range(args.batch)]
+    if args.what == "decode":
+        while any(r.pending > 1 or r.state != "running" for r in reqs):
+            engine.step()
+        for _ in range(3):
+            engine.step()
+    else:
+        warm = engine.add(torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist(),
+                          SamplingParams(max_tokens=1, ignore_eos=True))
+        engine.sched.waiting.remove(warm)
+        engine.sched.waiting.appendleft(warm)
+        engine.sched.max_admit = 1
+        engine.step()
+        engine.sched.max_admit = 64
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    a.record()
+    engine.step()
+    b.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"what": args.what, "shape": args.shape, "layers": layers, "batch": args.batch, "context": args.context,
+                      "graphs": not args.no_cuda_graphs, "step_ms": round(a.elapsed_time(b), 3)}), flush=True)
+    return 0
+
+
 def cmd_random_weights(args) -> int:
     from .config import Llama3RopeScaling, LlamaConfig
     from .weights import write_random_model
@@ -172,6 +231,16 @@ def main(argv: list[str] | None = None) -> int:
     b.add_argument("--prompts", type=int, default=80, help="number of distinct prompts")
     b.add_argument("--prompt-len", type=int, default=64)
     b.set_defaults(fn=cmd_bench)
+
+    pr = sub.add_parser("profile", help="one step at a named shape between cudaProfilerStart/Stop (for ncu)")
+    _engine_args(pr)
+    pr.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    pr.add_argument("--shape", choices=["8b", "3b", "1b"], default="8b")
+    pr.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (smaller captures)")
+    pr.add_argument("--batch", type=int, default=8)
+    pr.add_argument("--context", type=int, default=1024)
+    pr.add_argument("--what", choices=["decode", "prefill"], default="decode")
+    pr.set_defaults(fn=cmd_profile)
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     r.add_argument("--out", required=True)

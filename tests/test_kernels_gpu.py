@@ -339,7 +339,7 @@ def test_decode_attention_splits_and_counters(n_req, S):
     """Decode only, long enough that the keys are split over several blocks; run twice on the same
     scratch (the counters must come back to zero) and in the layout a captured graph uses."""
     nq, nkv, d, page = 8, 2, 128, 16
-    requests = [(S - 13 * r, 1, (S - 13 * r) // 2) for r in range(n_req)]
+    requests = [(S - 13 * (r % 5), 1, (S - 13 * (r % 5)) // 2) for r in range(n_req)]
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=n_req * (S // page + 2), seed=S)
     for graph in (False, True):
         ctx.extras = {"graph": True} if graph else {}
