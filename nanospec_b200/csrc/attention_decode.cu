@@ -296,3 +296,58 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
 #undef NS_DECODE_CASE
     NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d", d);
 }
+
+// ---------------------------------------------------------------------------------------
+// The same kernel for callers that must not allocate: its scratch lives in a fixed array of
+// the library image.  Declared and documented in nanospec_b200_noalloc.h.
+// ---------------------------------------------------------------------------------------
+#include "nanospec_b200_noalloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char ns_noalloc_scratch[NS_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_base[kMaxDevices] = {};  // device address of ns_noalloc_scratch, per device, found on first use
+
+size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
+}  // namespace
+
+NS_API int ns_attention_decode_noalloc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                       const int* block_table, int table_stride, const int* token_req,
+                                       const int* positions, const int* qo_indptr, void* out, int o_stride,
+                                       const int* rows, int n_tokens, int nq, int nkv, int head_dim, int page_size,
+                                       float scale, int window, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    if (nkv < 1 || nq < nkv || nq % nkv || n_splits < 1 || head_dim < 1)
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode_noalloc: nq=%d nkv=%d head_dim=%d n_splits=%d", nq, nkv, head_dim, n_splits);
+    long long o_floats, ml_floats, ctr_ints;
+    ns_attention_decode_scratch(n_tokens, nq, nkv, head_dim, n_splits, &o_floats, &ml_floats, &ctr_ints);
+    const size_t ctr_bytes = round256((size_t)ctr_ints * sizeof(int));
+    const size_t ml_bytes = round256((size_t)ml_floats * sizeof(float));
+    const size_t o_bytes = round256((size_t)o_floats * sizeof(float));
+    const size_t need = ctr_bytes + ml_bytes + o_bytes;
+    if (need > NS_NOALLOC_SCRATCH_BYTES)
+        NS_FAIL(NS_ERR_UNSUPPORTED,
+                "ns_attention_decode_noalloc: %d tokens x %d heads x %d splits x head_dim %d need %zu bytes of scratch; "
+                "the built-in array holds %u (use fewer splits or tokens, or ns_attention_decode with your own scratch)",
+                n_tokens, nq, n_splits, head_dim, need, NS_NOALLOC_SCRATCH_BYTES);
+    int dev = 0;
+    NS_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_noalloc: device %d", dev);
+    if (g_noalloc_base[dev] == nullptr) {
+        // set-up, once per device, with that device current: the array's address on this device
+        void* p = nullptr;
+        NS_CUDA(cudaGetSymbolAddress(&p, ns_noalloc_scratch));
+        g_noalloc_base[dev] = p;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_base[dev]);
+    int* counters = reinterpret_cast<int*>(base);
+    float* part_ml = reinterpret_cast<float*>(base + ctr_bytes);
+    float* part_o = reinterpret_cast<float*>(base + ctr_bytes + ml_bytes);
+    // the array keeps whatever the last call left: the arrival counters must start at zero
+    NS_CUDA(cudaMemsetAsync(counters, 0, ctr_bytes, stream));
+    return ns_attention_decode(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr,
+                               out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, head_dim, page_size,
+                               scale, window, n_splits, stream);
+}
