@@ -3,7 +3,7 @@
 // processed together so that every key and value is read from HBM once per group.
 //
 // Grid (split, kv head x head tile, token).  A block streams its share of the keys through
-// shared memory with cp.async (two stages of 64 keys), computes scores and the weighted sum on
+// shared memory with cp.async (three stages of 64 keys), computes scores and the weighted sum on
 // the tensor cores (m16n8k16, the group's heads padded to 16 rows), keeps the softmax in fp32
 // (online, base 2), and writes an unnormalised partial result with its running maximum and sum.
 // The block that finishes last for a (token, kv head) - found with an atomic counter - merges
@@ -16,6 +16,8 @@
 #include "attention_common.cuh"
 
 namespace {
+
+constexpr int kStages = 3;  // key/value tiles in flight per block
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
@@ -30,7 +32,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     constexpr int S = Tile::kStride;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* kv = qs + 16 * S;  // [stage][k|v][64][S]
+    __nv_bfloat16* kv = qs + 16 * S;  // [kStages][k|v][64][S]
     __shared__ int is_last;
 
     const int split = blockIdx.x, z = blockIdx.z;
@@ -62,8 +64,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             ns_cp_async16(Tile::at(qs, row, ch * 8), qrow + (valid ? (size_t)row * D + ch * 8 : 0), valid);
         }
     }
-    if (n_tiles > 0) load_kv_tile<D>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k0, kstart, k1, hk, nkv, page_size);
-    ns_cp_async_commit();
+    // the first kStages-1 tiles are requested up front; every iteration requests one more
+#pragma unroll
+    for (int st = 0; st < kStages - 1; ++st) {
+        if (st < n_tiles) {
+            __nv_bfloat16* kn = kv + (size_t)st * 2 * kTileKeys * S;
+            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size);
+        }
+        ns_cp_async_commit();
+    }
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[D / 8][4];
@@ -76,15 +85,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int mat = lane >> 3, r8 = lane & 7;
 
     for (int t = 0; t < n_tiles; ++t) {
-        __nv_bfloat16* ks = kv + (size_t)(t & 1) * 2 * kTileKeys * S;
+        __nv_bfloat16* ks = kv + (size_t)(t % kStages) * 2 * kTileKeys * S;
         __nv_bfloat16* vs = ks + kTileKeys * S;
-        if (t + 1 < n_tiles) {
-            __nv_bfloat16* kn = kv + (size_t)((t + 1) & 1) * 2 * kTileKeys * S;
-            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + 1) * kTileKeys, kstart, k1, hk, nkv, page_size);
+        ns_cp_async_wait<kStages - 2>();  // tile t has landed
+        __syncthreads();                  // ... for every thread, and every warp is done with tile t-1
+        if (t + kStages - 1 < n_tiles) {  // refill the stage that tile t-1 used
+            __nv_bfloat16* kn = kv + (size_t)((t + kStages - 1) % kStages) * 2 * kTileKeys * S;
+            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + kStages - 1) * kTileKeys, kstart, k1, hk,
+                            nkv, page_size);
         }
         ns_cp_async_commit();
-        ns_cp_async_wait<1>();
-        __syncthreads();
         if (t == 0) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk)
@@ -143,7 +153,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 ns_mma_bf16(o[2 * nb2 + 1], pa, vf[2], vf[3]);
             }
         }
-        __syncthreads();  // every warp is done with this stage before the copy after next overwrites it
     }
     ns_cp_async_wait<0>();
     __syncthreads();
@@ -239,7 +248,7 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
                   int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
     constexpr int S = NsTile<D>::kStride;
-    const size_t tiles = (size_t)(16 + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
+    const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
     const size_t smem = tiles > 16 * S * sizeof(__nv_bfloat16) + scratch ? tiles : 16 * S * sizeof(__nv_bfloat16) + scratch;
     static bool configured = false;

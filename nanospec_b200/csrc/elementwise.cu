@@ -93,11 +93,92 @@ add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, cons
     }
 }
 
+// Vector variant for widths that are a multiple of 8 with 16-byte aligned rows: every thread owns
+// CHUNKS groups of 8 consecutive elements, read and written with 16-byte accesses.
+__device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <typename T, int THREADS, int CHUNKS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
+                       T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+    __shared__ float scratch[32];
+    const int j = blockIdx.x;
+    const int row = rows ? rows[j] : j;
+    float* r = resid + (size_t)row * hidden;
+    const T* b = branch ? branch + (size_t)row * hidden : nullptr;
+    T* o = out + (size_t)j * hidden;
+    float v[CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int h = (threadIdx.x + c * THREADS) * 8;
+        if (h < hidden) {
+            ld8(r + h, v[c]);
+            if (b) {
+                float t[8];
+                ld8(b + h, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[c][i] += t[i];
+                if (write_resid) st8(r + h, v[c]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+        }
+    }
+    const float inv = rsqrtf(ns_block_sum(ss, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int h = (threadIdx.x + c * THREADS) * 8;
+        if (h < hidden) {
+            float g[8], y[8];
+            ld8(gain + h, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = v[c][i] * inv * g[i];
+            st8(o + h, y);
+        }
+    }
+}
+
 template <typename T>
 static int launch_add_rmsnorm(float* resid, const void* branch, const float* gain, void* out, const int* rows,
                               int n_rows, int hidden, float eps, int write_resid, cudaStream_t stream) {
     const T* b = (const T*)branch;
     T* o = (T*)out;
+    const bool aligned = hidden % 8 == 0 && (((uintptr_t)resid | (uintptr_t)branch | (uintptr_t)gain | (uintptr_t)out) % 16 == 0);
+    if (aligned && hidden >= 1024 && hidden <= 16384) {
+        // the sum of squares runs over the same elements in another grouping than the scalar kernel;
+        // which kernel runs depends on the width and alignment only, never on the batch
+        if (hidden <= 2048)
+            add_rmsnorm_vec_kernel<T, 128, 2><<<n_rows, 128, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        else if (hidden <= 4096)
+            add_rmsnorm_vec_kernel<T, 256, 2><<<n_rows, 256, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        else if (hidden <= 8192)
+            add_rmsnorm_vec_kernel<T, 512, 2><<<n_rows, 512, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        else
+            add_rmsnorm_vec_kernel<T, 1024, 2><<<n_rows, 1024, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_CHECK_LAUNCH("ns_add_rmsnorm");
+        return NS_OK;
+    }
     if (hidden <= 256)
         add_rmsnorm_kernel<T, 64, 4><<<n_rows, 64, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
     else if (hidden <= 1024)
@@ -160,9 +241,36 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     ns_st(out, i, (g / (1.f + expf(-g))) * u);
 }
 
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total8) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const int per_row = inter / 8;
+    const size_t n = i / per_row;
+    const int j = (int)(i - n * per_row) * 8;
+    float g[8], u[8], y[8];
+    ld8(gu + n * 2 * (size_t)inter + j, g);
+    ld8(gu + n * 2 * (size_t)inter + inter + j, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) y[k] = (g[k] / (1.f + expf(-g[k]))) * u[k];
+    st8(out + n * (size_t)inter + j, y);
+}
+
 NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)n_rows * inter;
     if (total == 0) return NS_OK;
+    if (inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) % 16 == 0)) {
+        const size_t total8 = total / 8;
+        const unsigned vblocks = (unsigned)((total8 + 255) / 256);
+        if (dtype == NS_F32)
+            swiglu_vec_kernel<float><<<vblocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total8);
+        else if (dtype == NS_BF16)
+            swiglu_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total8);
+        else
+            NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
+        NS_CHECK_LAUNCH("ns_swiglu");
+        return NS_OK;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == NS_F32)
         swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);

@@ -209,7 +209,7 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
 
 
 TILE_Q = 64          # query rows per block of the prefill kernel
-_TARGET_BLOCKS = 592  # decode attention aims at about four blocks per SM of a B200
+_TARGET_BLOCKS = 296  # decode attention aims at about two blocks per SM of a B200
 
 
 def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
@@ -223,7 +223,7 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
     head_tiles = -(-(nq // nkv) // 16)
     n_splits = max(1, min(16, -(-_TARGET_BLOCKS // (n_rows * nkv * head_tiles))))
     if max_kv_len is not None:
-        n_splits = max(1, min(n_splits, -(-max_kv_len // 64)))
+        n_splits = max(1, min(n_splits, -(-max_kv_len // 128)))  # at least two tiles of keys per split
     ws = ctx.workspace
     part_o = ws.get("attn_part_o", n_rows * nq * n_splits, head_dim, torch.float32)
     part_ml = ws.get("attn_part_ml", n_rows * nq * n_splits, 2, torch.float32)
