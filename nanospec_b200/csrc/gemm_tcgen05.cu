@@ -1,0 +1,386 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: out[M, N] = x[M, K] * w[N, K]^T.
+//
+// The product is computed transposed ("swap A/B"): the weight rows (output features) are the M
+// side of tcgen05.mma (128 per block, one TMEM lane each) and the tokens are its N side (16 to
+// 256 per block).  That keeps the tensor core's 128 lanes full for any number of tokens, so the
+// same kernel streams weights for a decode step of a few tokens and tiles a prompt of thousands.
+//
+// One block = 6 warps with fixed roles:
+//   warp 0, one lane: TMA producer.  Per 64-wide k block it waits for a free stage, arms the
+//           stage's mbarrier with the byte count and issues two cp.async.bulk.tensor loads (weight
+//           tile 128 x 64, token tile BN x 64) into 128-byte-swizzled shared memory.
+//   warp 1, one lane: MMA issuer.  Waits for a full stage, issues four tcgen05.mma (k = 16 each)
+//           with shared-memory descriptors, accumulating in TMEM, and commits to the stage's
+//           "empty" mbarrier so the producer may refill it; after the last k block it commits to
+//           the "accumulator ready" mbarrier.  Warp 1 also allocates and frees the TMEM columns.
+//   warps 2-5: epilogue.  Each warp reads its 32 TMEM lanes with tcgen05.ld and stores
+//           out[token, feature] (a warp writes 32 consecutive features of one token).
+// Split-K: with `splits` > 1 the k blocks are divided among blocks that write fp32 partial tiles;
+// the block that arrives last at the tile's counter adds the partials in split order (the result
+// does not depend on arrival order) and resets the counter.
+//
+// Every wait on an mbarrier is bounded (two seconds): when it runs out the thread records a code
+// in *error_flag and the block winds down (copies in flight are awaited, again bounded, TMEM is
+// freed).  The host reads the flag with ns_gemm_tc_error().
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;            // features per block = UMMA M
+constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 28;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // two seconds
+
+enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrainWait = 4 };
+
+template <int BN>
+struct Cfg {
+    // few tokens: 6 stages of 18-20 KB so that two blocks share an SM (12 tiles in flight per SM)
+    static constexpr int kStages = BN <= 32 ? 6 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4));
+    static constexpr int kMinBlocks = BN <= 32 ? 2 : 1;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// bounded wait: false when the limit ran out (the caller records the error and winds down).
+// The limit is kWaitLimitNs of wall time, checked every 1024 polls, and kSpinLimit polls at most.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// d (TMEM) (+)= a (smem) * b (smem)^T, bf16 inputs, fp32 accumulation
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) and are
+// stored with the 128-byte swizzle that TMA writes: 8-row groups are 1024 bytes apart (SBO), the
+// leading offset is unused for swizzled K-major tiles (1), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;              // leading byte offset (>>4), unused here
+    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset (>>4)
+    d |= (uint64_t)1 << 46;              // version
+    d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D = fp32, A = B = bf16, both K-major, M = 128, N = BN.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits,
+               float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ error_flag) {
+    using C = Cfg<BN>;
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+    const uint32_t bar_base = base + C::kStages * C::kStageBytes;
+    // barriers: full[kStages], empty[kStages], accum, then the TMEM address holder
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    const uint32_t accum_bar = bar_base + 8u * (2 * C::kStages);
+    const uint32_t holder = accum_bar + 8u;
+    __shared__ int is_last;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;      // first feature of the tile
+    const int tok0 = blockIdx.y * BN;    // first token of the tile
+    const int split = blockIdx.z;
+    // this block's k blocks
+    const int per = k_blocks / splits, rem = k_blocks % splits;
+    const int kb_begin = split * per + min(split, rem);
+    const int kb_count = per + (split < rem ? 1 : 0);
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(holder, C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        int issued = 0;
+        bool ok = true;
+        for (int i = 0; i < kb_count; ++i) {
+            const int s = i % C::kStages;
+            const uint32_t ph = (uint32_t)(i / C::kStages) & 1u;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; atomicExch(error_flag, kErrProducerWait); break; }
+            mbar_expect_tx(full_bar(s), C::kStageBytes);
+            const uint32_t a = base + s * C::kStageBytes;
+            tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, full_bar(s));
+            tma_load_2d(a + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(s));
+            ++issued;
+        }
+        if (!ok) {
+            // wait, bounded, for the copies that are still in flight before the block may exit
+            failed = 1;
+            for (int i = max(0, issued - C::kStages); i < issued; ++i)
+                if (!mbar_wait(full_bar(i % C::kStages), (uint32_t)(i / C::kStages) & 1u)) {
+                    atomicExch(error_flag, kErrDrainWait);
+                    break;
+                }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc = instr_desc<BN>();
+        for (int i = 0; i < kb_count; ++i) {
+            const int s = i % C::kStages;
+            const uint32_t ph = (uint32_t)(i / C::kStages) & 1u;
+            if (!mbar_wait(full_bar(s), ph)) { failed = 1; atomicExch(error_flag, kErrMmaWait); break; }
+            tc_fence_after();
+            const uint32_t a = base + s * C::kStageBytes;
+            const uint32_t b = a + C::kABytes;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_bf16(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                          (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+        }
+        umma_commit(accum_bar);         // the accumulator is complete once every MMA above has finished
+    } else if (warp >= 2) {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;  // the TMEM lane quarter this warp may read
+        const int f = n0 + q * 32 + lane;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(accum_bar, 0);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+            if (lane == 0) { failed = 1; atomicExch(error_flag, kErrEpilogueWait); }
+        } else {
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 8; ++c) {
+                if (tok0 + c * 8 >= M_tok) break;  // uniform across the warp
+                uint32_t r[8];
+                tmem_ld8(taddr + c * 8, r);
+                tmem_ld_wait();
+                if (f < N_feat) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int tok = tok0 + c * 8 + j;
+                        if (tok < M_tok) {
+                            const float v = __uint_as_float(r[j]);
+                            if (splits == 1) store_out(out + (size_t)tok * ldo + f, v);
+                            else partial[((size_t)split * M_tok + tok) * N_feat + f] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- wind down: free TMEM, then (split-K) let the last block reduce ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+    if (splits == 1 || failed) return;
+
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* ctr = counters + blockIdx.y * gridDim.x + blockIdx.x;
+        const int old = atomicAdd(ctr, 1);
+        is_last = (old == splits - 1);
+        if (is_last) *ctr = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < BM * BN; e += kThreads) {
+        const int j = e / BM, i = e - j * BM;  // consecutive threads take consecutive features
+        const int tok = tok0 + j, ff = n0 + i;
+        if (tok >= M_tok || ff >= N_feat) continue;
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) acc += __ldcg(partial + ((size_t)s * M_tok + tok) * N_feat + ff);
+        store_out(out + (size_t)tok * ldo + ff, acc);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// rows x K bf16 matrix with row stride ld (elements); box = box_rows x 64, 128-byte swizzle, zero fill
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) NS_FAIL(NS_ERR_CUDA, "ns_gemm_bf16_tc: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) NS_FAIL(NS_ERR_CUDA, "ns_gemm_bf16_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NS_OK;
+}
+
+template <int BN, typename OutT>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int M_tok, int N_feat, int k_blocks,
+              int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        NS_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+        configured = true;
+    }
+    dim3 grid((N_feat + BM - 1) / BM, (M_tok + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, OutT><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks,
+                                                                       splits, partial, counters, error_flag);
+    NS_CHECK_LAUNCH("ns_gemm_bf16_tc");
+    return NS_OK;
+}
+
+}  // namespace
+
+// Tokens per block the kernel would use for M_tok tokens, and the features per block.
+NS_API int ns_gemm_bf16_tc_tile(int M_tok, int* tokens_per_block, int* features_per_block) {
+    *tokens_per_block = M_tok <= 16 ? 16 : M_tok <= 32 ? 32 : M_tok <= 64 ? 64 : M_tok <= 128 ? 128 : 256;
+    *features_per_block = BM;
+    return NS_OK;
+}
+
+// out[M_tok, N_feat] (bf16 when out_f32 == 0, float otherwise, row stride ldo) =
+//     x[M_tok, K] (bf16, row stride ldx) * w[N_feat, K]^T (bf16, row stride ldw).
+// K, ldx and ldw must be multiples of 8 and the pointers 16-byte aligned (TMA); otherwise the call is
+// refused with NS_ERR_UNSUPPORTED.  splits > 1 needs `partial` (splits * M_tok * N_feat floats) and
+// `counters` (one int per output tile, zero before the first launch; left zero).  `error_flag` is a
+// device int that a timed-out wait sets (see ns_gemm_tc_error).
+NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
+                           int ldo, int out_f32, int splits, float* partial, int* counters, int* error_flag,
+                           cudaStream_t stream) {
+    if (M_tok <= 0 || N_feat <= 0) return NS_OK;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x | (uintptr_t)w) % 16)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: K=%d ldx=%d ldw=%d must be multiples of 8 and operands 16-byte aligned", K, ldx, ldw);
+    const int k_blocks = (K + BK - 1) / BK;
+    if (splits < 1 || splits > k_blocks || splits > 32)
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: splits=%d with %d k blocks", splits, k_blocks);
+    if (splits > 1 && (!partial || !counters)) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: split-K needs scratch");
+    if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: no error flag");
+    int bn, bm;
+    ns_gemm_bf16_tc_tile(M_tok, &bn, &bm);
+    if ((M_tok + bn - 1) / bn > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: too many token tiles");
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, N_feat, K, ldw, BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, M_tok, K, ldx, bn);
+    if (rc) return rc;
+#define NS_TC_CASE(BNN)                                                                                                 \
+    case BNN:                                                                                                           \
+        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, partial, counters,    \
+                                               error_flag, stream)                                                      \
+                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, partial,      \
+                                                       counters, error_flag, stream);
+    switch (bn) {
+        NS_TC_CASE(16) NS_TC_CASE(32) NS_TC_CASE(64) NS_TC_CASE(128) NS_TC_CASE(256)
+    }
+#undef NS_TC_CASE
+    NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: tile of %d tokens", bn);
+}

@@ -101,12 +101,87 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class _TensorCoreGemmState:
+    """Per-device scratch of the tcgen05 matrix product: the flag that a timed-out wait sets,
+    the split-K counters (left zero by every launch) and the split-K partial tiles.  Buffers that
+    have been handed to a launch are never freed (a captured graph may point into them)."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        self.partial = torch.empty(1 << 20, dtype=torch.float32, device=device)
+        self._retired: list[torch.Tensor] = []
+
+    def partial_for(self, floats: int) -> torch.Tensor:
+        if self.partial.numel() < floats:
+            self._retired.append(self.partial)
+            self.partial = torch.empty(max(floats, 2 * self.partial.numel()), dtype=torch.float32, device=self.device)
+        return self.partial
+
+
+_tc_state: dict[torch.device, _TensorCoreGemmState] = {}
+_SM_COUNT = 148
+USE_TENSOR_CORE_GEMM = True  # the hand-written tcgen05 kernel; False hands every bf16 product to cuBLAS
+
+
+def _tc(device: torch.device) -> _TensorCoreGemmState:
+    st = _tc_state.get(device)
+    if st is None:
+        st = _tc_state[device] = _TensorCoreGemmState(device)
+    return st
+
+
+def check_kernel_errors(device: torch.device | None = None) -> None:
+    """Raises if a kernel recorded a timed-out wait since the last check (one small device read)."""
+    for dev, st in _tc_state.items():
+        if device is not None and dev != device:
+            continue
+        code = int(st.error.item())
+        if code:
+            st.error.zero_()
+            what = {1: "the TMA producer waited for a free stage", 2: "the MMA issuer waited for a tile",
+                    3: "the epilogue waited for the accumulator", 4: "copies in flight did not land"}.get(code, "?")
+            raise KernelError(f"tcgen05 matrix product gave up after two seconds: {what} (code {code}); its output is not valid")
+
+
+def gemm_splits(M: int, N: int, K: int) -> int:
+    """How many blocks share the k range of one output tile: enough to occupy the SMs when the
+    output has few tiles (a decode step), 1 when it has many."""
+    tokens_per_block = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    tiles = -(-N // 128) * -(-M // tokens_per_block)
+    k_blocks = -(-K // 64)
+    resident = _SM_COUNT * (2 if tokens_per_block <= 32 else 1)
+    return max(1, min(8, resident // tiles, k_blocks // 8))
+
+
+def linear_tensor_core(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int | None = None) -> bool:
+    """The tcgen05 kernel (csrc/gemm_tcgen05.cu).  Returns False, having done nothing, when the
+    operands do not meet TMA's rules (K and the row strides multiples of 8 elements, 16-byte bases)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 \
+            or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    st = _tc(x.device)
+    if splits is None:
+        splits = gemm_splits(M, N, K)
+    partial = st.partial_for(splits * M * N) if splits > 1 else None
+    if splits > 1 and -(-N // 128) * -(-M // 16) > st.counters.numel():
+        splits, partial = 1, None
+    lib.call("ns_gemm_bf16_tc", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+             out.stride(0), int(out.dtype == torch.float32), splits, _ptr(partial), st.counters.data_ptr(),
+             st.error.data_ptr(), _stream())
+    return True
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T with fp32 accumulation.
 
     float32: the CUDA-core kernel (true fp32, k-ascending sums, independent of M).
-    bfloat16: a plain matrix product, handed to cuBLAS as the reference hands its
-    `nn.Linear` calls (model/llama.py:175,184,195); `out` may be bfloat16 or float32.
+    bfloat16: the tcgen05 kernel; operands that TMA cannot address (K or a row stride that is no
+    multiple of 8) are a plain matrix product for cuBLAS, as the reference hands its `nn.Linear`
+    calls to it (model/llama.py:175,184,195).  `out` may be bfloat16 or float32.
     """
     _cuda(x, w, out)
     M, K = x.shape
@@ -123,12 +198,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported operand types {x.dtype}, {w.dtype}")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"linear: unsupported output type {out.dtype}")
+    if USE_TENSOR_CORE_GEMM and linear_tensor_core(x, w, out):
+        return out
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
-    elif out.dtype == torch.float32:
-        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
-        raise KernelError(f"linear: unsupported output type {out.dtype}")
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     return out
 
 

@@ -1,0 +1,89 @@
+"""The tcgen05 matrix product alone against float64 arithmetic on the same bf16 inputs: few
+tokens (weight streaming), many tokens (tiled), sizes that are no multiple of any tile, split-K
+with its counters reused, float32 output, and operands that TMA cannot take (refused, then
+served by the fallback)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def ops():
+    from nanospec_b200 import ops as o
+    return o
+
+
+def case(M, N, K, seed, ldx=None, ldw=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, ldx or K, generator=g).to(torch.bfloat16).to(DEV)[:, :K]
+    w = torch.randn(N, ldw or K, generator=g).to(torch.bfloat16).to(DEV)[:, :K]
+    return x, w, x.double() @ w.double().T
+
+
+def check(out, want, K):
+    err = (out.double() - want).abs().max().item()
+    scale = want.abs().max().item()
+    tol = (2.0 ** -8 if out.dtype == torch.bfloat16 else 1e-5) * scale + 1e-4 * K ** 0.5
+    assert err <= tol, f"max |diff| {err} against tolerance {tol}"
+
+
+def test_smallest_tile_first():
+    x, w, want = case(8, 128, 64, 0)
+    out = torch.zeros(8, 128, dtype=torch.float32, device=DEV)
+    assert ops().linear_tensor_core(x, w, out, splits=1)
+    torch.cuda.synchronize()
+    ops().check_kernel_errors()
+    check(out, want, 64)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (1, 256, 256), (8, 6144, 4096), (3, 331, 96), (16, 128, 4096), (17, 200, 520), (40, 1000, 1024), (64, 4096, 1024),
+    (100, 384, 200), (130, 257, 72), (300, 512, 1024), (700, 1152, 2048), (2048, 1024, 512),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_against_float64(M, N, K, out_dtype):
+    x, w, want = case(M, N, K, M + N + K)
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device=DEV)
+    assert ops().linear_tensor_core(x, w, out, splits=1)
+    torch.cuda.synchronize()
+    ops().check_kernel_errors()
+    check(out, want, K)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 4096, 4), (1, 512, 14336, 7), (64, 384, 1024, 3), (20, 200, 520, 2), (8, 256, 8192, 8)])
+def test_split_k_is_deterministic_and_leaves_its_counters_zero(M, N, K, splits):
+    x, w, want = case(M, N, K, splits)
+    outs = []
+    for _ in range(3):
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        assert ops().linear_tensor_core(x, w, out, splits=splits)
+        outs.append(out)
+    torch.cuda.synchronize()
+    ops().check_kernel_errors()
+    check(outs[0], want, K)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    from nanospec_b200.ops import _tc
+    assert int(_tc(x.device).counters.sum()) == 0
+
+
+def test_strided_rows_and_output():
+    x, w, want = case(24, 192, 128, 5, ldx=136, ldw=256)
+    wide = torch.zeros(24, 400, dtype=torch.bfloat16, device=DEV)
+    out = wide[:, 100:292]
+    assert ops().linear_tensor_core(x, w, out, splits=1)
+    torch.cuda.synchronize()
+    check(out, want, 128)
+    assert float(wide[:, :100].abs().max()) == 0 and float(wide[:, 292:].abs().max()) == 0
+
+
+def test_operands_tma_cannot_take_fall_back():
+    x, w, want = case(5, 64, 100, 9)  # K = 100 is no multiple of 8
+    out = torch.zeros(5, 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops().linear_tensor_core(x, w, out)
+    ops().linear(x.contiguous(), w.contiguous(), out)
+    check(out, want, 100)
+    assert ops().gemm_splits(8, 4096, 4096) > 1 and ops().gemm_splits(2048, 4096, 4096) == 1
