@@ -28,6 +28,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
                         int n_splits, int head_tiles) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
     constexpr int S = Tile::kStride;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -258,7 +260,7 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
     }
     const int G = nq / nkv, head_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * head_tiles, n_tokens);
-    attention_decode_kernel<D><<<grid, kThreads, smem, stream>>>(
+    NS_LAUNCH((attention_decode_kernel<D>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
         nkv, page_size, scale, window, n_splits, head_tiles);

@@ -22,6 +22,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_req, const int* __restrict__ positions, T* __restrict__ out,
                          int o_stride, int n_tokens, int nq, int nkv, int d, int page_size, float scale, int window) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     extern __shared__ float qsm[];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long long w = (long long)blockIdx.x * kWarpsPerBlock + wib;
@@ -96,7 +98,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     const int dpl = (d + 31) / 32;
 #define NS_ATTN_CASE(D)                                                                                              \
     case D:                                                                                                          \
-        attention_generic_kernel<T, D><<<blocks, kWarpsPerBlock * 32, smem, stream>>>(                               \
+        NS_LAUNCH((attention_generic_kernel<T, D>), blocks, kWarpsPerBlock * 32, smem, stream,                                \
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride, token_req,       \
             positions, (T*)out, o_stride, n_tokens, nq, nkv, d, page_size, scale, window);                           \
         break;

@@ -24,6 +24,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
                          int page_size, float scale, int window) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
     constexpr int S = Tile::kStride;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -191,7 +193,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
         configured = true;
     }
     dim3 grid(n_tiles, nq);
-    attention_prefill_kernel<D><<<grid, kThreads, smem, stream>>>(
+    NS_LAUNCH((attention_prefill_kernel<D>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window);
     NS_CHECK_LAUNCH("ns_attention_prefill");

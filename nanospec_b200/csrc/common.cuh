@@ -87,3 +87,32 @@ __device__ __forceinline__ float ns_block_max(float v, float* scratch) {
     __syncthreads();
     return scratch[0];
 }
+
+// ---- launches ------------------------------------------------------------------------------
+// Every kernel of this library is launched with programmatic stream serialisation allowed: a
+// kernel may be scheduled while its predecessor in the stream is still running, and it calls
+// ns_pdl_wait() before it touches anything the predecessor wrote (or writes anything the
+// predecessor may read).  What runs before that wait - barrier set-up, TMEM allocation, the first
+// weight tiles of a matrix product - overlaps the predecessor.  ns_set_pdl(0) turns this off.
+extern int ns_pdl_enabled;
+
+__device__ __forceinline__ void ns_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ns_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t ns_launch_impl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ns_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define NS_LAUNCH(kernel, grid, block, smem, stream, ...) \
+    (void)ns_launch_impl(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)

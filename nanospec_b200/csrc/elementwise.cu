@@ -8,12 +8,22 @@
 thread_local char ns_error_text[512] = "";
 NS_API const char* ns_last_error() { return ns_error_text; }
 
+int ns_pdl_enabled = 1;
+// 1 (default): kernels are launched so that they may overlap the tail of their predecessor
+// (programmatic dependent launch); 0: plain stream order.
+NS_API int ns_set_pdl(int enabled) {
+    ns_pdl_enabled = enabled ? 1 : 0;
+    return NS_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // embedding: out[n, :] = float(table[ids[n], :]); a negative id (padding row) gives zeros
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     const int n = blockIdx.x;
     const int id = ids[n];
     float* o = out + (size_t)n * hidden;
@@ -30,9 +40,9 @@ NS_API int ns_embed(const void* table, const int* ids, float* out, int n_tokens,
     if (n_tokens <= 0) return NS_OK;
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     if (dtype == NS_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+        NS_LAUNCH((embed_kernel<float>), n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
     else if (dtype == NS_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+        NS_LAUNCH((embed_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_embed: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_embed");
@@ -51,6 +61,8 @@ template <typename T, int THREADS, int PER_THREAD>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
                    T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float scratch[32];
     const int j = blockIdx.x;
     const int row = rows ? rows[j] : j;
@@ -121,6 +133,8 @@ template <typename T, int THREADS, int CHUNKS>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float scratch[32];
     const int j = blockIdx.x;
     const int row = rows ? rows[j] : j;
@@ -169,24 +183,24 @@ static int launch_add_rmsnorm(float* resid, const void* branch, const float* gai
         // the sum of squares runs over the same elements in another grouping than the scalar kernel;
         // which kernel runs depends on the width and alignment only, never on the batch
         if (hidden <= 2048)
-            add_rmsnorm_vec_kernel<T, 128, 2><<<n_rows, 128, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 128, 2>), n_rows, 128, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
         else if (hidden <= 4096)
-            add_rmsnorm_vec_kernel<T, 256, 2><<<n_rows, 256, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 256, 2>), n_rows, 256, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
         else if (hidden <= 8192)
-            add_rmsnorm_vec_kernel<T, 512, 2><<<n_rows, 512, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 512, 2>), n_rows, 512, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
         else
-            add_rmsnorm_vec_kernel<T, 1024, 2><<<n_rows, 1024, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 1024, 2>), n_rows, 1024, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
         NS_CHECK_LAUNCH("ns_add_rmsnorm");
         return NS_OK;
     }
     if (hidden <= 256)
-        add_rmsnorm_kernel<T, 64, 4><<<n_rows, 64, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_LAUNCH((add_rmsnorm_kernel<T, 64, 4>), n_rows, 64, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
     else if (hidden <= 1024)
-        add_rmsnorm_kernel<T, 128, 8><<<n_rows, 128, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_LAUNCH((add_rmsnorm_kernel<T, 128, 8>), n_rows, 128, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
     else if (hidden <= 4096)
-        add_rmsnorm_kernel<T, 512, 8><<<n_rows, 512, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_LAUNCH((add_rmsnorm_kernel<T, 512, 8>), n_rows, 512, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
     else
-        add_rmsnorm_kernel<T, 1024, 8><<<n_rows, 1024, 0, stream>>>(resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_LAUNCH((add_rmsnorm_kernel<T, 1024, 8>), n_rows, 1024, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
     NS_CHECK_LAUNCH("ns_add_rmsnorm");
     return NS_OK;
 }
@@ -208,6 +222,8 @@ NS_API int ns_add_rmsnorm(float* resid, const void* branch, const float* gain, v
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ resid, const T* __restrict__ branch, size_t n) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += ns_ld(branch, i);
 }
@@ -217,9 +233,9 @@ NS_API int ns_residual_add(float* resid, const void* branch, int n_rows, int hid
     if (n == 0) return NS_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == NS_F32)
-        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(resid, (const float*)branch, n);
+        NS_LAUNCH((residual_add_kernel<float>), blocks, 256, 0, stream, resid, (const float*)branch, n);
     else if (dtype == NS_BF16)
-        residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(resid, (const __nv_bfloat16*)branch, n);
+        NS_LAUNCH((residual_add_kernel<__nv_bfloat16>), blocks, 256, 0, stream, resid, (const __nv_bfloat16*)branch, n);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_residual_add: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_residual_add");
@@ -232,6 +248,8 @@ NS_API int ns_residual_add(float* resid, const void* branch, int n_rows, int hid
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t n = i / inter;
@@ -243,6 +261,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total8) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total8) return;
     const int per_row = inter / 8;
@@ -263,9 +283,9 @@ NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int 
         const size_t total8 = total / 8;
         const unsigned vblocks = (unsigned)((total8 + 255) / 256);
         if (dtype == NS_F32)
-            swiglu_vec_kernel<float><<<vblocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total8);
+            NS_LAUNCH((swiglu_vec_kernel<float>), vblocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total8);
         else if (dtype == NS_BF16)
-            swiglu_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total8);
+            NS_LAUNCH((swiglu_vec_kernel<__nv_bfloat16>), vblocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total8);
         else
             NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
         NS_CHECK_LAUNCH("ns_swiglu");
@@ -273,9 +293,9 @@ NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int 
     }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == NS_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+        NS_LAUNCH((swiglu_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
     else if (dtype == NS_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        NS_LAUNCH((swiglu_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_swiglu");

@@ -13,6 +13,8 @@ template <bool kAligned>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int N, int K,
                 int ldx, int ldw, int ldy) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -101,9 +103,9 @@ NS_API int ns_gemm_f32(const float* x, const float* w, float* y, int M, int N, i
     if (grid.y > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_f32: M=%d exceeds 65535 row tiles", M);
     const bool aligned = (ldx % 4 == 0) && (ldw % 4 == 0) && (((uintptr_t)x | (uintptr_t)w) % 16 == 0);
     if (aligned)
-        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldw, ldy);
+        NS_LAUNCH((gemm_f32_kernel<true>), grid, 256, 0, stream, x, w, y, M, N, K, ldx, ldw, ldy);
     else
-        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldw, ldy);
+        NS_LAUNCH((gemm_f32_kernel<false>), grid, 256, 0, stream, x, w, y, M, N, K, ldx, ldw, ldy);
     NS_CHECK_LAUNCH("ns_gemm_f32");
     return NS_OK;
 }

@@ -161,6 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ int is_last;
     __shared__ int failed;
 
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled; it waits for this one before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BM;      // first feature of the tile
     const int tok0 = blockIdx.y * BN;    // first token of the tile
@@ -189,9 +190,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
+        // The weights do not depend on the previous kernel: their first tiles are requested before
+        // this kernel waits for it, so they stream in while the predecessor is still running.  The
+        // token tiles of those stages follow after the wait (each stage's barrier counts both).
         int issued = 0;
         bool ok = true;
-        for (int i = 0; i < kb_count; ++i) {
+        const int early = min(kb_count, C::kStages);
+        for (int i = 0; i < early; ++i) {
+            mbar_expect_tx(full_bar(i), C::kStageBytes);
+            tma_load_2d(base + i * C::kStageBytes, &map_w, (kb_begin + i) * BK, n0, full_bar(i));
+        }
+        ns_pdl_wait();
+        for (int i = 0; i < early; ++i) {
+            tma_load_2d(base + i * C::kStageBytes + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(i));
+            ++issued;
+        }
+        for (int i = early; i < kb_count; ++i) {
             const int s = i % C::kStages;
             const uint32_t ph = (uint32_t)(i / C::kStages) & 1u;
             if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; atomicExch(error_flag, kErrProducerWait); break; }
@@ -229,6 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(accum_bar);         // the accumulator is complete once every MMA above has finished
     } else if (warp >= 2) {
         // ---------------- epilogue ----------------
+        ns_pdl_wait();           // before anything is written that the previous kernel may still read
         const int q = warp & 3;  // the TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;
         bool ok = true;
@@ -332,7 +347,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, 
         configured = true;
     }
     dim3 grid((N_feat + BM - 1) / BM, (M_tok + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, OutT><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks,
+    NS_LAUNCH((gemm_tc_kernel<BN, OutT>), grid, kThreads, C::kSmemBytes, stream, mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks,
                                                                        splits, partial, counters, error_flag);
     NS_CHECK_LAUNCH("ns_gemm_bf16_tc");
     return NS_OK;

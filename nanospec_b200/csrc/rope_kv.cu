@@ -19,6 +19,8 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
                      const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d,
                      int rot_pairs, int write_kv) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     const int n = blockIdx.x, hh = blockIdx.y;
     const int req = token_req[n];
     if (req < 0) return;
@@ -62,11 +64,11 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
     const dim3 grid(n_tokens, nq + 2 * nkv);
     const int threads = d / 2 <= 32 ? 32 : (d / 2 <= 64 ? 64 : 128);
     if (dtype == NS_F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
+        NS_LAUNCH((rope_kv_write_kernel<float>), grid, threads, 0, stream, 
             (float*)qkv, positions, token_req, block_table, table_stride, inv_freq, (float*)k_cache, (float*)v_cache,
             page_size, nq, nkv, d, rot_pairs, write_kv);
     else if (dtype == NS_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        NS_LAUNCH((rope_kv_write_kernel<__nv_bfloat16>), grid, threads, 0, stream, 
             (__nv_bfloat16*)qkv, positions, token_req, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, rot_pairs, write_kv);
     else

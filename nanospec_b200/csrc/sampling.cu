@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ u,
                    int* __restrict__ token, float* __restrict__ logprob_raw, float* __restrict__ logprob_proc) {
+    ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float fscratch[32];
     __shared__ int iscratch[32];
     __shared__ float seg_prefix[kThreads];
@@ -276,7 +278,7 @@ NS_API int ns_sample_rows(const float* logits, long long ld, int n_rows, int voc
                           float* logprob_proc, cudaStream_t stream) {
     if (n_rows <= 0) return NS_OK;
     if (vocab <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_sample_rows: vocab=%d", vocab);
-    sample_rows_kernel<<<n_rows, kThreads, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, u, token,
+    NS_LAUNCH((sample_rows_kernel), n_rows, kThreads, 0, stream, logits, ld, vocab, temperature, top_k, top_p, u, token,
                                                        logprob_raw, logprob_proc);
     NS_CHECK_LAUNCH("ns_sample_rows");
     return NS_OK;

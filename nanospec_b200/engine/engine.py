@@ -76,6 +76,7 @@ class Engine:
         reqs = [self.add(p, sp) for p, sp in zip(prompts, plist)]
         while self.sched.has_work:
             self.step()
+        ops.check_kernel_errors(self.device)
         return [r.out_tokens for r in reqs]
 
     def _emit(self, req: Request, info: TokenInfo) -> bool:
@@ -117,6 +118,8 @@ class Engine:
                 self.sched.finish(req)
                 finished.append(req)
         self.steps += 1
+        if self.steps % 64 == 0:
+            ops.check_kernel_errors(self.device)  # a timed-out wait inside a kernel must not pass silently
         self._flush_prof()
         return finished
 

@@ -39,6 +39,7 @@ def main(argv: list[str] | None = None) -> int:
     if 64 % args.block_size:
         ap.error("--block-size must divide 64")
 
+    from .. import ops
     from ..ops import lib
     from ..weights import load_model
     from .step import ModelRunner, StepEntry
@@ -74,6 +75,7 @@ def main(argv: list[str] | None = None) -> int:
             logits = runner.step(entries)
             if logits is not None:
                 host = logits.to("cpu", torch.float32).contiguous()
+                ops.check_kernel_errors()
                 (out_dir / f"{step}.f32").write_bytes(host.numpy().astype("<f4", copy=False).tobytes())
         for name in rec.get("end", []):
             name = str(name)

@@ -123,6 +123,10 @@ class _TensorCoreGemmState:
 _tc_state: dict[torch.device, _TensorCoreGemmState] = {}
 _SM_COUNT = 148
 USE_TENSOR_CORE_GEMM = True  # the hand-written tcgen05 kernel; False hands every bf16 product to cuBLAS
+# Products with more tokens than this go to cuBLAS, whose kernels are ahead of the hand-written
+# one there (measured: 68-85 % of cuBLAS at 2,048 tokens, behind it at 64 because of split-K
+# traffic); None = no limit.
+TENSOR_CORE_GEMM_MAX_TOKENS: int | None = 16
 
 
 def _tc(device: torch.device) -> _TensorCoreGemmState:
@@ -130,6 +134,11 @@ def _tc(device: torch.device) -> _TensorCoreGemmState:
     if st is None:
         st = _tc_state[device] = _TensorCoreGemmState(device)
     return st
+
+
+def set_programmatic_launch(enabled: bool) -> None:
+    """Kernels may overlap the tail of their predecessor in the stream (default on)."""
+    lib.call("ns_set_pdl", int(bool(enabled)))
 
 
 def check_kernel_errors(device: torch.device | None = None) -> None:
@@ -200,7 +209,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise KernelError(f"linear: unsupported operand types {x.dtype}, {w.dtype}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"linear: unsupported output type {out.dtype}")
-    if USE_TENSOR_CORE_GEMM and linear_tensor_core(x, w, out):
+    if USE_TENSOR_CORE_GEMM and (TENSOR_CORE_GEMM_MAX_TOKENS is None or M <= TENSOR_CORE_GEMM_MAX_TOKENS) \
+            and linear_tensor_core(x, w, out):
         return out
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
