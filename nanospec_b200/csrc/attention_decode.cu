@@ -18,6 +18,7 @@
 namespace {
 
 constexpr int kStages = 3;  // key/value tiles in flight per block
+constexpr int kMaxSplits = 16;
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
@@ -230,15 +231,24 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         const int row = e / D, col = e - row * D;
         const int h = h0 + row;
         const size_t base = ((size_t)z * nq + h) * n_splits;
+        // every split's maximum, sum and partial value are requested together, then combined in split order
+        float ms[kMaxSplits], ls[kMaxSplits], os[kMaxSplits];
+#pragma unroll
+        for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+            const bool on = s2 < n_splits;
+            ms[s2] = on ? __ldcg(part_ml + (base + s2) * 2) : -INFINITY;
+            ls[s2] = on ? __ldcg(part_ml + (base + s2) * 2 + 1) : 0.f;
+            os[s2] = on ? __ldcg(part_o + (base + s2) * D + col) : 0.f;
+        }
         float mt = -INFINITY;
-        for (int s2 = 0; s2 < n_splits; ++s2) mt = fmaxf(mt, __ldcg(part_ml + (base + s2) * 2));
+#pragma unroll
+        for (int s2 = 0; s2 < kMaxSplits; ++s2) mt = fmaxf(mt, ms[s2]);
         float acc = 0.f, lt = 0.f;
-        for (int s2 = 0; s2 < n_splits; ++s2) {
-            const float ms = __ldcg(part_ml + (base + s2) * 2);
-            if (ms == -INFINITY) continue;  // an empty split
-            const float f = exp2f(ms - mt);
-            acc += __ldcg(part_o + (base + s2) * D + col) * f;
-            lt += __ldcg(part_ml + (base + s2) * 2 + 1) * f;
+#pragma unroll
+        for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+            const float f = ms[s2] == -INFINITY ? 0.f : exp2f(ms[s2] - mt);  // an empty split adds nothing
+            acc += os[s2] * f;
+            lt += ls[s2] * f;
         }
         out[(size_t)n * o_stride + (size_t)h * D + col] = __float2bfloat16_rn(acc / lt);
     }
@@ -292,7 +302,7 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
     if (d % 16 || d < 16 || d > 128)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d (multiples of 16 up to 128)", d);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: %d query heads over %d kv heads", nq, nkv);
-    if (n_splits < 1 || n_splits > 64) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: n_splits=%d (1..64)", n_splits);
+    if (n_splits < 1 || n_splits > kMaxSplits) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: n_splits=%d (1..%d)", n_splits, kMaxSplits);
     if (q_stride % 8 || ((uintptr_t)q % 16)) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: q rows must be 16-byte aligned");
     if (n_tokens > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: %d tokens exceed the grid's z extent", n_tokens);
 #define NS_DECODE_CASE(DD)                                                                                             \

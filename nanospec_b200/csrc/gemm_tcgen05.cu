@@ -32,6 +32,7 @@ constexpr int BM = 128;            // features per block = UMMA M
 constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
+constexpr int kMaxSplits = 8;
 constexpr uint32_t kSpinLimit = 1u << 28;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // two seconds
 
@@ -295,13 +296,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int e = threadIdx.x; e < BM * BN; e += kThreads) {
+    // one (token, feature) per thread and pass; the partials of all splits are requested together
+    // (independent loads) and added in split order
+    const int tok_n = min(BN, M_tok - tok0), feat_n = min(BM, N_feat - n0);
+    for (int e = threadIdx.x; e < tok_n * BM; e += kThreads) {
         const int j = e / BM, i = e - j * BM;  // consecutive threads take consecutive features
-        const int tok = tok0 + j, ff = n0 + i;
-        if (tok >= M_tok || ff >= N_feat) continue;
+        if (i >= feat_n) continue;
+        const size_t at = ((size_t)(tok0 + j)) * N_feat + n0 + i;
+        const size_t plane = (size_t)M_tok * N_feat;
+        float v[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? __ldcg(partial + s * plane + at) : 0.f;
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += __ldcg(partial + ((size_t)s * M_tok + tok) * N_feat + ff);
-        store_out(out + (size_t)tok * ldo + ff, acc);
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
+        store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
     }
 }
 
@@ -375,7 +384,7 @@ NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, i
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x | (uintptr_t)w) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: K=%d ldx=%d ldw=%d must be multiples of 8 and operands 16-byte aligned", K, ldx, ldw);
     const int k_blocks = (K + BK - 1) / BK;
-    if (splits < 1 || splits > k_blocks || splits > 32)
+    if (splits < 1 || splits > k_blocks || splits > kMaxSplits)
         NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: splits=%d with %d k blocks", splits, k_blocks);
     if (splits > 1 && (!partial || !counters)) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: split-K needs scratch");
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: no error flag");
