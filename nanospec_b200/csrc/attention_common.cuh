@@ -13,19 +13,21 @@ constexpr float kLog2e = 1.4426950408889634f;
 // Rows key0 .. key0+63 of one kv head: cache[page, offset, hk, :] with page = bt[key / page_size].
 // Rows before key_lo (their pages may already have been given back behind a window) and rows at or
 // beyond key_end are not read but zero-filled (a masked weight of zero must not meet a NaN).
-template <int D>
+template <int D, int THREADS = kThreads>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const __nv_bfloat16* k_cache,
                                              const __nv_bfloat16* v_cache, const int* bt, int key0, int key_lo, int key_end,
-                                             int hk, int nkv, int page_size) {
+                                             int hk, int nkv, int page_size, int page_shift) {
     constexpr int kChunks = D / 8;
-    for (int c = threadIdx.x; c < kTileKeys * kChunks; c += kThreads) {
+    for (int c = threadIdx.x; c < kTileKeys * kChunks; c += THREADS) {
         const int row = c / kChunks, ch = c - row * kChunks;
         const int key = key0 + row;
         const bool valid = key >= key_lo && key < key_end;
         size_t off = 0;
         if (valid) {
-            const int page = bt[key / page_size];
-            off = (((size_t)page * page_size + key % page_size) * nkv + hk) * D + ch * 8;
+            // page_shift >= 0: the page size is a power of two (no integer division per row)
+            const int blk = page_shift >= 0 ? key >> page_shift : key / page_size;
+            const int within = page_shift >= 0 ? key & (page_size - 1) : key - blk * page_size;
+            off = (((size_t)bt[blk] * page_size + within) * nkv + hk) * D + ch * 8;
         }
         ns_cp_async16(NsTile<D>::at(ks, row, ch * 8), k_cache + off, valid);
         ns_cp_async16(NsTile<D>::at(vs, row, ch * 8), v_cache + off, valid);

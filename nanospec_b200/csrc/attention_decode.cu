@@ -56,6 +56,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int n_tiles = k0 < k1 ? (k1 - k0 + kTileKeys - 1) / kTileKeys : 0;
     const int* bt = block_table + (size_t)req * table_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
     // ---- q of the group's heads (rows beyond the group are zero) and the first tile ----------
     {
@@ -72,7 +73,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     for (int st = 0; st < kStages - 1; ++st) {
         if (st < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)st * 2 * kTileKeys * S;
-            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size);
+            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size, page_shift);
         }
         ns_cp_async_commit();
     }
@@ -95,7 +96,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (t + kStages - 1 < n_tiles) {  // refill the stage that tile t-1 used
             __nv_bfloat16* kn = kv + (size_t)((t + kStages - 1) % kStages) * 2 * kTileKeys * S;
             load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + kStages - 1) * kTileKeys, kstart, k1, hk,
-                            nkv, page_size);
+                            nkv, page_size, page_shift);
         }
         ns_cp_async_commit();
         if (t == 0) {

@@ -2,8 +2,8 @@
 // token per request), causal and aligned to absolute positions, so a portion that continues a
 // request attends to everything the request has in the cache plus its own earlier tokens.
 //
-// Grid (query tile, query head).  A query tile is 64 consecutive tokens of one request, given
-// by the host as (request, offset into the request's tokens of this step); each of the 4 warps
+// Grid (query tile, query head).  A query tile is 128 consecutive tokens of one request, given
+// by the host as (request, offset into the request's tokens of this step); each of the 8 warps
 // owns 16 query rows.  Keys and values of the head's kv head stream through shared memory with
 // cp.async in tiles of 64 (two stages); scores and the weighted sum run on the tensor cores
 // (m16n8k16), the softmax is online in fp32 (base 2).  A query at position p sees keys
@@ -15,10 +15,11 @@
 
 namespace {
 
-constexpr int kTileQ = 64;
+constexpr int kTileQ = 128;        // query rows per block: 8 warps of 16 rows
+constexpr int kPrefillThreads = 256;
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kPrefillThreads)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
@@ -45,17 +46,18 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int n_tiles = (kend - k_begin + kTileKeys - 1) / kTileKeys;
     const int* bt = block_table + (size_t)req * table_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
     {
         constexpr int kChunks = D / 8;
         const __nv_bfloat16* qbase = q + (size_t)tok0 * q_stride + (size_t)h * D;
-        for (int c = tid; c < kTileQ * kChunks; c += kThreads) {
+        for (int c = tid; c < kTileQ * kChunks; c += kPrefillThreads) {
             const int row = c / kChunks, ch = c - row * kChunks;
             const bool valid = row < rows;
             ns_cp_async16(Tile::at(qs, row, ch * 8), qbase + (valid ? (size_t)row * q_stride + ch * 8 : 0), valid);
         }
     }
-    load_kv_tile<D>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size);
+    load_kv_tile<D, kPrefillThreads>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size, page_shift);
     ns_cp_async_commit();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -79,8 +81,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         __nv_bfloat16* vs = ks + kTileKeys * S;
         if (t + 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + 1) & 1) * 2 * kTileKeys * S;
-            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k_begin + (t + 1) * kTileKeys, kfirst, kend, hk,
-                            nkv, page_size);
+            load_kv_tile<D, kPrefillThreads>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k_begin + (t + 1) * kTileKeys, kfirst, kend, hk,
+                            nkv, page_size, page_shift);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<1>();
@@ -108,17 +110,31 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 }
             }
             float mx[2] = {-INFINITY, -INFINITY};
+            // tiles that lie wholly inside every row's visible range need no mask
+            const int warp_pos_min = pos0 + min(warp * 16, rows - 1);
+            const bool full = kb + kTileKeys - 1 <= warp_pos_min && (window <= 0 || kb > warp_pos_max - window);
+            if (full) {
 #pragma unroll
-            for (int nb = 0; nb < 8; ++nb)
+                for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int key = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
-                    const int p = prow[j >> 1];
-                    const bool seen = key <= p && (window <= 0 || key > p - window);
-                    const float v = seen ? s[nb][j] * sl : -INFINITY;
-                    s[nb][j] = v;
-                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
-                }
+                    for (int j = 0; j < 4; ++j) {
+                        const float v = s[nb][j] * sl;
+                        s[nb][j] = v;
+                        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                    }
+            } else {
+#pragma unroll
+                for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int key = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
+                        const int p = prow[j >> 1];
+                        const bool seen = key <= p && (window <= 0 || key > p - window);
+                        const float v = seen ? s[nb][j] * sl : -INFINITY;
+                        s[nb][j] = v;
+                        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                    }
+            }
             float corr[2], m_use[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -193,7 +209,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
         configured = true;
     }
     dim3 grid(n_tiles, nq);
-    NS_LAUNCH((attention_prefill_kernel<D>), grid, kThreads, smem, stream, 
+    NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window);
     NS_CHECK_LAUNCH("ns_attention_prefill");
@@ -203,7 +219,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 }  // namespace
 
 // tiles: int32 [n_tiles, 2] = (request, offset of the tile's first token among the request's
-// tokens of this step, a multiple of 64).  bfloat16 only; head_dim a multiple of 16 up to 128.
+// tokens of this step, a multiple of 128).  bfloat16 only; head_dim a multiple of 16 up to 128.
 NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
                                 const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,

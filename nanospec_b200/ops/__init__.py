@@ -295,7 +295,7 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
                   head_dim, write_kv=True)
 
 
-TILE_Q = 64          # query rows per block of the prefill kernel
+TILE_Q = 128         # query rows per block of the prefill kernel
 _TARGET_BLOCKS = 296  # decode attention aims at about two blocks per SM of a B200
 
 

@@ -326,7 +326,7 @@ def test_tensor_core_attention_mixed_step(nq, nkv, d, page, window):
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=2000 // page + 40, seed=d + nq)
     out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
     ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), window)
-    assert ctx.extras["attention_plan"]["n_decode"] == 4 and ctx.extras["attention_plan"]["tiles"].shape[0] == 3 + 2 + 1 + 3
+    assert ctx.extras["attention_plan"]["n_decode"] == 4 and ctx.extras["attention_plan"]["tiles"].shape[0] == 2 + 1 + 1 + 2
     row = 0
     for (S, q_len, _), (q, k, v, start) in zip(requests, want):
         full = plain.plain_attention(q, k, v, window=window)
