@@ -15,13 +15,13 @@
 //           the "accumulator ready" mbarrier.  Warp 1 also allocates and frees the TMEM columns.
 //   warps 2-5: epilogue.  Each warp reads its 32 TMEM lanes with tcgen05.ld and stores
 //           out[token, feature] (a warp writes 32 consecutive features of one token).
-// Split-K: with `splits` > 1 the k blocks are divided among blocks that write fp32 partial tiles;
-// the block that arrives last at the tile's counter adds the partials in split order (the result
-// does not depend on arrival order) and resets the counter.
+// Split-K: with `splits` in {2, 4, 8} the k blocks of one output tile are divided among the blocks
+// of a thread-block cluster; each leaves its fp32 partial tile in its shared memory and, after a
+// cluster barrier, adds one slice of the features from all blocks' shared memory in rank order.
 //
 // Every wait on an mbarrier is bounded (two seconds): when it runs out the thread records a code
 // in *error_flag and the block winds down (copies in flight are awaited, again bounded, TMEM is
-// freed).  The host reads the flag with ns_gemm_tc_error().
+// freed).  The host reads the flag after the stream has been synchronised.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -142,6 +142,19 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a float from the shared memory of block `rank` of this cluster, at the address that `local` has here
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
 __device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
@@ -149,7 +162,7 @@ template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits,
-               float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ error_flag) {
+               int* __restrict__ error_flag) {
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -159,8 +172,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
     const uint32_t accum_bar = bar_base + 8u * (2 * C::kStages);
     const uint32_t holder = accum_bar + 8u;
-    __shared__ int is_last;
     __shared__ int failed;
+    // after the last MMA the pipeline stages are free: the split-K partial tile is staged there
+    float* stage_f32 = reinterpret_cast<float*>(smem_dyn + (base - smem_u32(smem_dyn)));
 
     ns_pdl_launch_dependents();  // the next kernel may be scheduled; it waits for this one before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -268,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
                             if (splits == 1) store_out(out + (size_t)tok * ldo + f, v);
-                            else partial[((size_t)split * M_tok + tok) * N_feat + f] = v;
+                            else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
                 }
@@ -276,42 +290,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     }
 
-    // ---------------- wind down: free TMEM, then (split-K) let the last block reduce ----------------
+    // ---------------- wind down: free TMEM; with split-K the blocks of the cluster add their tiles ----------------
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
-    if (splits == 1 || failed) return;
+    if (splits == 1) return;
 
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* ctr = counters + blockIdx.y * gridDim.x + blockIdx.x;
-        const int old = atomicAdd(ctr, 1);
-        is_last = (old == splits - 1);
-        if (is_last) *ctr = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // one (token, feature) per thread and pass; the partials of all splits are requested together
-    // (independent loads) and added in split order
-    const int tok_n = min(BN, M_tok - tok0), feat_n = min(BM, N_feat - n0);
-    for (int e = threadIdx.x; e < tok_n * BM; e += kThreads) {
-        const int j = e / BM, i = e - j * BM;  // consecutive threads take consecutive features
-        if (i >= feat_n) continue;
-        const size_t at = ((size_t)(tok0 + j)) * N_feat + n0 + i;
-        const size_t plane = (size_t)M_tok * N_feat;
-        float v[kMaxSplits];
+    // The `splits` blocks of one output tile form a thread-block cluster.  Each has left its fp32
+    // partial tile in its own shared memory; after a cluster barrier every block adds, in rank
+    // order, one slice of the features from all the blocks' shared memory (distributed shared
+    // memory) and writes that slice of the result.  Nothing goes through global memory, and the
+    // sum does not depend on timing.  Blocks that gave up still take part in both barriers.
+    cluster_sync();
+    if (!failed) {
+        const int tok_n = min(BN, M_tok - tok0);
+        const int slice = BM / splits;             // features this block reduces
+        const int i0 = split * slice;
+        const uint32_t stage_addr = smem_u32(stage_f32);
+        for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
+            const int j = e / slice, i = i0 + (e - j * slice);
+            if (n0 + i >= N_feat) continue;
+            float v[kMaxSplits];
 #pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? __ldcg(partial + s * plane + at) : 0.f;
-        float acc = 0.f;
+            for (int s = 0; s < kMaxSplits; ++s)
+                v[s] = s < splits ? ld_cluster_f32(stage_addr + 4u * (uint32_t)(j * BM + i), (uint32_t)s) : 0.f;
+            float acc = 0.f;
 #pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
-        store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+            for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
+            store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+        }
     }
+    cluster_sync();  // no block may exit while another still reads its shared memory
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -348,7 +360,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 
 template <int BN, typename OutT>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int M_tok, int N_feat, int k_blocks,
-              int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {
+              int splits, int* error_flag, cudaStream_t stream) {
     using C = Cfg<BN>;
     static bool configured = false;
     if (!configured) {
@@ -356,8 +368,29 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, 
         configured = true;
     }
     dim3 grid((N_feat + BM - 1) / BM, (M_tok + BN - 1) / BN, splits);
-    NS_LAUNCH((gemm_tc_kernel<BN, OutT>), grid, kThreads, C::kSmemBytes, stream, mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks,
-                                                                       splits, partial, counters, error_flag);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (ns_pdl_enabled) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (splits > 1) {  // the blocks that share an output tile form a cluster along z
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = splits;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    (void)cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, OutT>, mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks, splits,
+                             error_flag);
     NS_CHECK_LAUNCH("ns_gemm_bf16_tc");
     return NS_OK;
 }
@@ -374,19 +407,16 @@ NS_API int ns_gemm_bf16_tc_tile(int M_tok, int* tokens_per_block, int* features_
 // out[M_tok, N_feat] (bf16 when out_f32 == 0, float otherwise, row stride ldo) =
 //     x[M_tok, K] (bf16, row stride ldx) * w[N_feat, K]^T (bf16, row stride ldw).
 // K, ldx and ldw must be multiples of 8 and the pointers 16-byte aligned (TMA); otherwise the call is
-// refused with NS_ERR_UNSUPPORTED.  splits > 1 needs `partial` (splits * M_tok * N_feat floats) and
-// `counters` (one int per output tile, zero before the first launch; left zero).  `error_flag` is a
-// device int that a timed-out wait sets (see ns_gemm_tc_error).
+// refused with NS_ERR_UNSUPPORTED.  splits is 1, 2, 4 or 8 (blocks of a cluster that share the k range).
+// `error_flag` is a device int that a timed-out wait sets.
 NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
-                           int ldo, int out_f32, int splits, float* partial, int* counters, int* error_flag,
-                           cudaStream_t stream) {
+                           int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
     if (M_tok <= 0 || N_feat <= 0) return NS_OK;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x | (uintptr_t)w) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: K=%d ldx=%d ldw=%d must be multiples of 8 and operands 16-byte aligned", K, ldx, ldw);
     const int k_blocks = (K + BK - 1) / BK;
-    if (splits < 1 || splits > k_blocks || splits > kMaxSplits)
-        NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: splits=%d with %d k blocks", splits, k_blocks);
-    if (splits > 1 && (!partial || !counters)) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: split-K needs scratch");
+    if (splits < 1 || splits > k_blocks || splits > kMaxSplits || (splits & (splits - 1)))
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: splits=%d with %d k blocks (1, 2, 4 or 8, at most the k blocks)", splits, k_blocks);
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: no error flag");
     int bn, bm;
     ns_gemm_bf16_tc_tile(M_tok, &bn, &bm);
@@ -398,10 +428,9 @@ NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, i
     if (rc) return rc;
 #define NS_TC_CASE(BNN)                                                                                                 \
     case BNN:                                                                                                           \
-        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, partial, counters,    \
-                                               error_flag, stream)                                                      \
-                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, partial,      \
-                                                       counters, error_flag, stream);
+        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, error_flag, stream)   \
+                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, error_flag,   \
+                                                       stream);
     switch (bn) {
         NS_TC_CASE(16) NS_TC_CASE(32) NS_TC_CASE(64) NS_TC_CASE(128) NS_TC_CASE(256)
     }

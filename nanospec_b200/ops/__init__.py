@@ -102,22 +102,11 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 class _TensorCoreGemmState:
-    """Per-device scratch of the tcgen05 matrix product: the flag that a timed-out wait sets,
-    the split-K counters (left zero by every launch) and the split-K partial tiles.  Buffers that
-    have been handed to a launch are never freed (a captured graph may point into them)."""
+    """Per-device state of the tcgen05 matrix product: the flag that a timed-out wait sets."""
 
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
-        self.counters = torch.zeros(4096, dtype=torch.int32, device=device)
-        self.partial = torch.empty(1 << 20, dtype=torch.float32, device=device)
-        self._retired: list[torch.Tensor] = []
-
-    def partial_for(self, floats: int) -> torch.Tensor:
-        if self.partial.numel() < floats:
-            self._retired.append(self.partial)
-            self.partial = torch.empty(max(floats, 2 * self.partial.numel()), dtype=torch.float32, device=self.device)
-        return self.partial
 
 
 _tc_state: dict[torch.device, _TensorCoreGemmState] = {}
@@ -161,7 +150,8 @@ def gemm_splits(M: int, N: int, K: int) -> int:
     tiles = -(-N // 128) * -(-M // tokens_per_block)
     k_blocks = -(-K // 64)
     resident = _SM_COUNT * (2 if tokens_per_block <= 32 else 1)
-    return max(1, min(8, resident // tiles, k_blocks // 8))
+    want = max(1, min(8, resident // tiles, k_blocks // 8))
+    return 1 << (want.bit_length() - 1)  # the blocks of a tile form a cluster of 1, 2, 4 or 8
 
 
 def linear_tensor_core(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int | None = None) -> bool:
@@ -175,12 +165,8 @@ def linear_tensor_core(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, spli
     st = _tc(x.device)
     if splits is None:
         splits = gemm_splits(M, N, K)
-    partial = st.partial_for(splits * M * N) if splits > 1 else None
-    if splits > 1 and -(-N // 128) * -(-M // 16) > st.counters.numel():
-        splits, partial = 1, None
     lib.call("ns_gemm_bf16_tc", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0),
-             out.stride(0), int(out.dtype == torch.float32), splits, _ptr(partial), st.counters.data_ptr(),
-             st.error.data_ptr(), _stream())
+             out.stride(0), int(out.dtype == torch.float32), splits, st.error.data_ptr(), _stream())
     return True
 
 
