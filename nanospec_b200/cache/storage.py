@@ -1,6 +1,8 @@
 """Device memory behind the cache manager: pages of keys and values per group and the
 per-request state tensors.  The reference's counterpart is `PagedKVCache`
-(kv/cache.py:13-26): K and V as [layers, pages, page_size, kv_heads, head_dim], zero-filled."""
+(kv/cache.py:13-26): K and V as [layers, pages, page_size, kv_heads, head_dim], zero-filled; here
+the kv head comes before the offset in the page, so that the keys a thread block streams (one
+kv head) lie in runs of page_size * head_dim elements instead of head_dim."""
 
 from __future__ import annotations
 
@@ -19,8 +21,8 @@ class CacheStorage:
         self.group_kv: list[torch.Tensor] = []
         for g in manager.groups:
             s = g.spec
-            # [lane in group, k|v, page, offset, kv head, dim]
-            self.group_kv.append(torch.zeros((len(s.lanes), 2, manager.num_blocks, s.page_size, s.kv_heads, s.head_dim),
+            # [lane in group, k|v, page, kv head, offset, dim]: one kv head's tokens of a page are contiguous
+            self.group_kv.append(torch.zeros((len(s.lanes), 2, manager.num_blocks, s.kv_heads, s.page_size, s.head_dim),
                                              dtype=dtype, device=device))
         self.state: dict[int, torch.Tensor] = {}
         for lane, (_, st) in enumerate(lane_needs):

@@ -10,7 +10,7 @@ constexpr int kTileKeys = 64;
 constexpr int kThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 
-// Rows key0 .. key0+63 of one kv head: cache[page, offset, hk, :] with page = bt[key / page_size].
+// Rows key0 .. key0+63 of one kv head: cache[page, hk, offset, :] with page = bt[key / page_size].
 // Rows before key_lo (their pages may already have been given back behind a window) and rows at or
 // beyond key_end are not read but zero-filled (a masked weight of zero must not meet a NaN).
 template <int D, int THREADS = kThreads>
@@ -27,7 +27,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
             // page_shift >= 0: the page size is a power of two (no integer division per row)
             const int blk = page_shift >= 0 ? key >> page_shift : key / page_size;
             const int within = page_shift >= 0 ? key & (page_size - 1) : key - blk * page_size;
-            off = (((size_t)bt[blk] * page_size + within) * nkv + hk) * D + ch * 8;
+            off = (((size_t)bt[blk] * nkv + hk) * page_size + within) * D + ch * 8;
         }
         ns_cp_async16(NsTile<D>::at(ks, row, ch * 8), k_cache + off, valid);
         ns_cp_async16(NsTile<D>::at(vs, row, ch * 8), v_cache + off, valid);

@@ -8,7 +8,7 @@
 //
 // A query at position p of request r sees the keys at positions max(0, p - window + 1) .. p
 // of the same request (window == 0: all of 0 .. p).  Keys and values are read from
-// cache[page, offset, kv_head, :] with page = block_table[r, position / page_size]; the
+// cache[page, kv_head, offset, :] with page = block_table[r, position / page_size]; the
 // step's own keys have been written before this kernel runs.  kv_head = q_head / (nq / nkv).
 #include "common.cuh"
 
@@ -55,8 +55,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         float s = -INFINITY;
         if (valid) {
             const int page = bt[key / page_size];
-            slot = (unsigned)page * (unsigned)page_size + (unsigned)(key % page_size);
-            const T* kr = k_cache + ((size_t)slot * nkv + hk) * d;
+            // row of cache[page, kv head, offset, :]
+            slot = ((unsigned)page * (unsigned)nkv + (unsigned)hk) * (unsigned)page_size + (unsigned)(key % page_size);
+            const T* kr = k_cache + (size_t)slot * d;
             float dot = 0.f;
             for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ns_ld(kr, e), dot);
             s = dot * scale;
@@ -71,7 +72,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         for (int j = 0; j < cnt; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const unsigned sj = __shfl_sync(0xffffffffu, slot, j);
-            const T* vr = v_cache + ((size_t)sj * nkv + hk) * d;
+            const T* vr = v_cache + (size_t)sj * d;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int e = lane + 32 * i;

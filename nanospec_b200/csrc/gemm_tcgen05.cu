@@ -40,9 +40,9 @@ enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kE
 
 template <int BN>
 struct Cfg {
-    // few tokens: 6 stages of 18-20 KB so that two blocks share an SM (12 tiles in flight per SM)
-    static constexpr int kStages = BN <= 32 ? 6 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4));
-    static constexpr int kMinBlocks = BN <= 32 ? 2 : 1;
+    // up to 64 tokens: stages sized so that two blocks share an SM (8 to 12 tiles in flight per SM)
+    static constexpr int kStages = BN <= 32 ? 6 : (BN == 64 ? 4 : (BN == 128 ? 6 : 4));
+    static constexpr int kMinBlocks = BN <= 64 ? 2 : 1;
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;

@@ -5,7 +5,7 @@
 // out[j+d/2] = x[j+d/2] cos + x[j] sin.  q is rotated in place in the packed projection
 // [q | k | v]; the rotated k and the untouched v go to the cache slot that the request's
 // block table gives for the token's position:
-//   page = block_table[request, position / page_size],  slot = page * page_size + position % page_size.
+//   page = block_table[request, position / page_size],  cache[page, kv head, position % page_size, :].
 // A token whose request index is negative is a padding row and is skipped.
 #include "common.cuh"
 
@@ -32,9 +32,9 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
     T* dst = x;
     if (!is_q) {
         const int page = block_table[(size_t)req * table_stride + pos / page_size];
-        const size_t slot = (size_t)page * page_size + pos % page_size;
         const int hk = is_v ? hh - nq - nkv : hh - nq;
-        dst = (is_v ? v_cache : k_cache) + (slot * nkv + hk) * d;
+        // cache[page, kv head, offset, :]
+        dst = (is_v ? v_cache : k_cache) + (((size_t)page * nkv + hk) * page_size + pos % page_size) * d;
     }
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         const float x1 = ns_ld(x, j), x2 = ns_ld(x, j + half);

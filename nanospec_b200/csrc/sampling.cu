@@ -55,10 +55,65 @@ __device__ int block_count_key_gt(const RowArgs& r, float temp, unsigned tau, in
     return iscratch[0];
 }
 
+constexpr int kChunks = 16;        // blocks that share one row in the first pass
+constexpr int kPartialThreads = 256;
+
+// First pass, (row, chunk) per block: maximum, its lowest index, and the sum of exp(z - maximum)
+// over one sixteenth of the vocabulary.  The row kernel merges the sixteen results, so a greedy row
+// needs no pass of its own over the logits.  partial[row][chunk] = {max, sum, index as float bits}.
+__global__ void __launch_bounds__(kPartialThreads)
+sample_partial_kernel(const float* __restrict__ logits, long long ld, int vocab, float* __restrict__ partial) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    __shared__ float fscratch[32];
+    __shared__ float smax[32];
+    __shared__ int sidx[32];
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const float* z = logits + (size_t)row * ld;
+    const int per = (vocab + kChunks - 1) / kChunks;
+    const int lo = min(chunk * per, vocab), hi = min(lo + per, vocab);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int i = lo + tid; i < hi; i += kPartialThreads) {
+        const float v = z[i];
+        if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    if (lane == 0) { smax[warp] = best; sidx[warp] = besti; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < kPartialThreads / 32 ? smax[lane] : -INFINITY;
+        besti = lane < kPartialThreads / 32 ? sidx[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if (lane == 0) { smax[0] = best; sidx[0] = besti; }
+    }
+    __syncthreads();
+    const float cmax = smax[0];
+    float se = 0.f;
+    for (int i = lo + tid; i < hi; i += kPartialThreads) se += expf(z[i] - cmax);
+    const float total = ns_block_sum(se, fscratch);
+    if (tid == 0) {
+        float* p = partial + ((size_t)row * kChunks + chunk) * 3;
+        p[0] = cmax;
+        p[1] = lo < hi ? total : 0.f;
+        p[2] = __int_as_float(sidx[0]);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ u,
-                   int* __restrict__ token, float* __restrict__ logprob_raw, float* __restrict__ logprob_proc) {
+                   const float* __restrict__ partial, int* __restrict__ token, float* __restrict__ logprob_raw,
+                   float* __restrict__ logprob_proc) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float fscratch[32];
@@ -73,38 +128,29 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     const float* z = logits + (size_t)row * ld;
     const RowArgs r{z, vocab};
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    (void)lane;
 
-    // ---- raw max, argmax (lowest index on ties) and log-sum-exp -------------------------
-    float best = -INFINITY;
-    int besti = 0x7fffffff;
-    for (int i = tid; i < vocab; i += kThreads) {
-        const float v = z[i];
-        if (v > best || (v == best && i < besti)) { best = v; besti = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
-    }
-    if (lane == 0) { smax[warp] = best; sidx[warp] = besti; }
-    __syncthreads();
-    if (warp == 0) {
-        best = smax[lane];
-        besti = sidx[lane];
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    // ---- raw max, argmax (lowest index on ties) and log-sum-exp: merged from the first pass ------
+    if (tid == 0) {
+        const float* p = partial + (size_t)row * kChunks * 3;
+        float best = -INFINITY;
+        int besti = 0x7fffffff;
+        for (int c = 0; c < kChunks; ++c) {  // chunks are in index order: the first maximum wins a tie
+            const float v = p[3 * c];
+            if (v > best) { best = v; besti = __float_as_int(p[3 * c + 2]); }
         }
-        if (lane == 0) { smax[0] = best; sidx[0] = besti; }
+        float se = 0.f;
+        for (int c = 0; c < kChunks; ++c)
+            if (p[3 * c + 1] > 0.f) se += p[3 * c + 1] * expf(p[3 * c] - best);
+        smax[0] = best;
+        sidx[0] = besti;
+        fscratch[1] = logf(se) + best;
     }
     __syncthreads();
     const float zmax = smax[0];
     const int amax = sidx[0];
-
-    float se = 0.f;
-    for (int i = tid; i < vocab; i += kThreads) se += expf(z[i] - zmax);
-    const float lse_raw = logf(ns_block_sum(se, fscratch)) + zmax;
+    const float lse_raw = fscratch[1];
+    __syncthreads();  // fscratch is reused by the block sums below
 
     const float temp = temperature[row];
     if (!(temp > 0.f)) {  // greedy
@@ -273,13 +319,16 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
 
 }  // namespace
 
+// `partial`: scratch of n_rows * 16 * 3 floats for the first pass.
 NS_API int ns_sample_rows(const float* logits, long long ld, int n_rows, int vocab, const float* temperature,
-                          const int* top_k, const float* top_p, const float* u, int* token, float* logprob_raw,
-                          float* logprob_proc, cudaStream_t stream) {
+                          const int* top_k, const float* top_p, const float* u, float* partial, int* token,
+                          float* logprob_raw, float* logprob_proc, cudaStream_t stream) {
     if (n_rows <= 0) return NS_OK;
     if (vocab <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_sample_rows: vocab=%d", vocab);
-    NS_LAUNCH((sample_rows_kernel), n_rows, kThreads, 0, stream, logits, ld, vocab, temperature, top_k, top_p, u, token,
-                                                       logprob_raw, logprob_proc);
+    if (!partial) NS_FAIL(NS_ERR_ARGUMENT, "ns_sample_rows: no scratch for the first pass");
+    NS_LAUNCH((sample_partial_kernel), dim3(n_rows, kChunks), kPartialThreads, 0, stream, logits, ld, vocab, partial);
+    NS_LAUNCH((sample_rows_kernel), n_rows, kThreads, 0, stream, logits, ld, vocab, temperature, top_k, top_p, u,
+              (const float*)partial, token, logprob_raw, logprob_proc);
     NS_CHECK_LAUNCH("ns_sample_rows");
     return NS_OK;
 }

@@ -56,6 +56,7 @@ class _Bucket:
         self.out_lp = torch.zeros(2, size, dtype=torch.float32, device=runner.device)
         self.out_host = torch.zeros(3, size, dtype=torch.float32).pin_memory()
         self.logits = torch.zeros(size, runner.model.vocab_size, dtype=torch.float32, device=runner.device)
+        self.sample_scratch = torch.zeros(size * 48, dtype=torch.float32, device=runner.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         # fixed parts of the description
         self.host_np[self.off["qo_indptr"]: self.off["qo_indptr"] + size + 1] = np.arange(size + 1, dtype=np.int32)
@@ -98,7 +99,7 @@ class _Bucket:
         hidden = runner.model.forward(self.ctx, self.want_rows)
         z = runner.model.logits(hidden, self.logits)
         t, k, p, u = self.sampling
-        ops.sample_rows(z, t, k, p, u, out=(self.out_token, self.out_lp[0], self.out_lp[1]))
+        ops.sample_rows(z, t, k, p, u, out=(self.out_token, self.out_lp[0], self.out_lp[1]), scratch=self.sample_scratch)
 
     def _capture(self, runner: ModelRunner, pool) -> None:
         # two eager runs on a side stream first (every row is padding, nothing touches the cache),

@@ -149,7 +149,7 @@ def gemm_splits(M: int, N: int, K: int) -> int:
     tokens_per_block = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // tokens_per_block)
     k_blocks = -(-K // 64)
-    resident = _SM_COUNT * (2 if tokens_per_block <= 32 else 1)
+    resident = _SM_COUNT * (2 if tokens_per_block <= 64 else 1)
     want = max(1, min(8, resident // tiles, k_blocks // 8))
     return 1 << (want.bit_length() - 1)  # the blocks of a tile form a cluster of 1, 2, 4 or 8
 
@@ -247,10 +247,11 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-                u: torch.Tensor, out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None
-                ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                u: torch.Tensor, out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+                scratch: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Per row of fp32 logits: (token int32, raw log-prob, processed log-prob); `out` gives
-    preallocated result tensors (int32, float32, float32, one entry per row)."""
+    preallocated result tensors (int32, float32, float32, one entry per row) and `scratch` a
+    preallocated float32 buffer of 48 floats per row for the kernel's first pass."""
     _cuda(logits, temperature, top_k, top_p, u)
     _i32(top_k, "top_k")
     rows, vocab = logits.shape
@@ -268,9 +269,13 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
         token = torch.empty(rows, dtype=torch.int32, device=logits.device)
         lp_raw = torch.empty(rows, dtype=torch.float32, device=logits.device)
         lp_proc = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    if scratch is None:
+        scratch = torch.empty(rows * 48, dtype=torch.float32, device=logits.device)
+    elif scratch.dtype != torch.float32 or scratch.numel() < rows * 48 or not scratch.is_contiguous():
+        raise KernelError("sample_rows: scratch must be contiguous float32 with 48 entries per row")
     lib.call("ns_sample_rows", logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
-             top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(), token.data_ptr(), lp_raw.data_ptr(), lp_proc.data_ptr(),
-             _stream())
+             top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(), scratch.data_ptr(), token.data_ptr(), lp_raw.data_ptr(),
+             lp_proc.data_ptr(), _stream())
     return token, lp_raw, lp_proc
 
 

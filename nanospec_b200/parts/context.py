@@ -12,7 +12,7 @@ import torch
 class LaneView:
     """One cache lane as a mixer sees it during a step."""
 
-    k: torch.Tensor | None            # [pages, page_size, kv_heads, head_dim]
+    k: torch.Tensor | None            # [pages, kv_heads, page_size, head_dim]
     v: torch.Tensor | None
     block_table: torch.Tensor | None  # [requests, max_pages] int32: page of each logical block
     page_size: int

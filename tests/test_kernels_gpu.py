@@ -111,12 +111,12 @@ def paged(k: torch.Tensor, v: torch.Tensor, page: int, n_pages: int, seed: int):
     g = torch.Generator().manual_seed(seed)
     nb = -(-S // page)
     pages = torch.randperm(n_pages, generator=g)[:nb]
-    kc = torch.zeros(n_pages, page, nkv, d, dtype=k.dtype)
-    vc = torch.zeros(n_pages, page, nkv, d, dtype=k.dtype)
+    kc = torch.zeros(n_pages, nkv, page, d, dtype=k.dtype)  # cache[page, kv head, offset, :]
+    vc = torch.zeros(n_pages, nkv, page, d, dtype=k.dtype)
     for b in range(nb):
         lo, hi = b * page, min(S, (b + 1) * page)
-        kc[pages[b], : hi - lo] = k[lo:hi]
-        vc[pages[b], : hi - lo] = v[lo:hi]
+        kc[pages[b], :, : hi - lo] = k[lo:hi].transpose(0, 1)
+        vc[pages[b], :, : hi - lo] = v[lo:hi].transpose(0, 1)
     return kc, vc, pages.to(torch.int32)
 
 
@@ -138,7 +138,7 @@ def test_rope_kv_write(dtype, nq, nkv, d, page):
     positions.insert(3, 0), token_req.insert(3, -1)  # a padding row in the middle
     N = len(positions)
     qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g).to(dtype)
-    kc = torch.zeros(n_pages, page, nkv, d, dtype=dtype, device=DEV)
+    kc = torch.zeros(n_pages, nkv, page, d, dtype=dtype, device=DEV)  # cache[page, kv head, offset, :]
     vc = torch.zeros_like(kc)
     dev_qkv = qkv.clone().to(DEV)
     ops().rope_kv_write(dev_qkv, torch.tensor(positions, dtype=torch.int32, device=DEV),
@@ -157,11 +157,11 @@ def test_rope_kv_write(dtype, nq, nkv, d, page):
         torch.testing.assert_close(got[n, : nq * d].view(nq, d), q_want[n], **tol(dtype))
         pg = int(tables_big[token_req[n], positions[n] // page])
         off = positions[n] % page
-        torch.testing.assert_close(kc[pg, off].float().cpu(), k_want[n], **tol(dtype))
-        assert torch.equal(vc[pg, off].float().cpu(), v_in[n])
+        torch.testing.assert_close(kc[pg, :, off].float().cpu(), k_want[n], **tol(dtype))
+        assert torch.equal(vc[pg, :, off].float().cpu(), v_in[n])
         # v and the unrotated part of the row stay as they were
         assert torch.equal(got[n, nq * d:], f[n, nq * d:])
-    assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) == sum(lens)  # nothing else was written
+    assert int((kc != 0).any(dim=-1).any(dim=1).sum()) == sum(lens)  # nothing else was written
 
 
 def attention_case(dtype, nq, nkv, d, page, S, window, spike_key=None, seed=0):
@@ -214,7 +214,7 @@ def test_attention_generic_batch_of_requests_and_padding():
     nq, nkv, d, page = 4, 2, 32, 8
     cases = [attention_case(dtype, nq, nkv, d, page, S, 0, spike, seed=S) for S, spike in ((33, 2), (8, None), (100, 50))]
     n_pages = 64
-    kc = torch.zeros(n_pages, page, nkv, d)
+    kc = torch.zeros(n_pages, nkv, page, d)
     vc = torch.zeros_like(kc)
     tables = torch.zeros(3, 16, dtype=torch.int32)
     free = list(torch.randperm(n_pages, generator=torch.Generator().manual_seed(5)).tolist())
@@ -224,7 +224,7 @@ def test_attention_generic_batch_of_requests_and_padding():
             pg = free.pop()
             tables[r, b] = pg
             lo, hi = b * page, min(S, (b + 1) * page)
-            kc[pg, : hi - lo], vc[pg, : hi - lo] = k[lo:hi], v[lo:hi]
+            kc[pg, :, : hi - lo], vc[pg, :, : hi - lo] = k[lo:hi].transpose(0, 1), v[lo:hi].transpose(0, 1)
     q_lens = [1, 8, 13]
     rows, positions, token_req, want = [], [], [], []
     for r, ((q, k, v, w), n) in enumerate(zip(cases, q_lens)):
@@ -287,7 +287,7 @@ def _step(requests, nq, nkv, d, page, n_pages, seed):
     flattened step; returns (ctx, lane, qkv rows, expected outputs per request)."""
     from types import SimpleNamespace
     from nanospec_b200.parts import Workspace
-    kc = torch.zeros(n_pages, page, nkv, d, dtype=torch.bfloat16)
+    kc = torch.zeros(n_pages, nkv, page, d, dtype=torch.bfloat16)
     vc = torch.zeros_like(kc)
     free = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
     width = max(-(-S // page) for S, _, _ in requests)
@@ -299,7 +299,7 @@ def _step(requests, nq, nkv, d, page, n_pages, seed):
             pg = free.pop()
             tables[r, b] = pg
             lo, hi = b * page, min(S, (b + 1) * page)
-            kc[pg, : hi - lo], vc[pg, : hi - lo] = k[lo:hi], v[lo:hi]
+            kc[pg, :, : hi - lo], vc[pg, :, : hi - lo] = k[lo:hi].transpose(0, 1), v[lo:hi].transpose(0, 1)
         rows.append(q[S - q_len:].reshape(q_len, nq * d))
         positions += list(range(S - q_len, S))
         token_req += [r] * q_len
