@@ -129,7 +129,7 @@ def prime(eng, batch: int, context: int, max_tokens: int, seed: int = 0):
     vocab = eng.model.vocab_size
     reqs = [eng.add(torch.randint(0, vocab, (context - 1,), generator=g).tolist(),
                     SamplingParams(max_tokens=max_tokens, ignore_eos=True)) for _ in range(batch)]
-    while any(r.pending > 1 or r.state != "running" for r in reqs):
+    while any(r.state == "waiting" or (r.state == "running" and r.pending > 1) for r in reqs):
         eng.step()
     return reqs
 

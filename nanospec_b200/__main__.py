@@ -150,14 +150,14 @@ def cmd_profile(args) -> int:
     model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
     args.max_running = max(args.batch, 1)
     args.max_admit = 64
-    pages = args.batch * (-(-(args.context + 64) // args.block_size) + 1) + 8
+    pages = args.batch * (-(-(args.context + 256) // args.block_size) + 1) + 8
     engine = _engine(model, args, pages)
     g = torch.Generator().manual_seed(0)
     n_prompt = args.context - 1 if args.what == "decode" else args.context
     reqs = [engine.add(torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist(),
-                       SamplingParams(max_tokens=32 if args.what == "decode" else 1, ignore_eos=True)) for _ in range(args.batch)]
+                       SamplingParams(max_tokens=256 if args.what == "decode" else 1, ignore_eos=True)) for _ in range(args.batch)]
     if args.what == "decode":
-        while any(r.pending > 1 or r.state != "running" for r in reqs):
+        while any(r.state == "waiting" or (r.state == "running" and r.pending > 1) for r in reqs):
             engine.step()
         for _ in range(3):
             engine.step()

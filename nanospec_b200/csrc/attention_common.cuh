@@ -18,16 +18,30 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
                                              const __nv_bfloat16* v_cache, const int* bt, int key0, int key_lo, int key_end,
                                              int hk, int nkv, int page_size, int page_shift) {
     constexpr int kChunks = D / 8;
-    for (int c = threadIdx.x; c < kTileKeys * kChunks; c += THREADS) {
+    constexpr int kItems = (kTileKeys * kChunks + THREADS - 1) / THREADS;  // 16-byte pieces per thread and tensor
+    // first the block-table entries of all of this thread's rows (independent loads), then the copies:
+    // the copies are ordered against other memory operations, and a table lookup between two of them
+    // would cost a full load latency each time
+    int page[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        const int key = key0 + c / kChunks;
+        const bool valid = c < kTileKeys * kChunks && key >= key_lo && key < key_end;
+        // page_shift >= 0: the page size is a power of two (no integer division per row)
+        page[i] = valid ? __ldg(bt + (page_shift >= 0 ? key >> page_shift : key / page_size)) : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        if (c >= kTileKeys * kChunks) break;
         const int row = c / kChunks, ch = c - row * kChunks;
         const int key = key0 + row;
-        const bool valid = key >= key_lo && key < key_end;
+        const bool valid = page[i] >= 0;
         size_t off = 0;
         if (valid) {
-            // page_shift >= 0: the page size is a power of two (no integer division per row)
-            const int blk = page_shift >= 0 ? key >> page_shift : key / page_size;
-            const int within = page_shift >= 0 ? key & (page_size - 1) : key - blk * page_size;
-            off = (((size_t)bt[blk] * nkv + hk) * page_size + within) * D + ch * 8;
+            const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+            off = (((size_t)page[i] * nkv + hk) * page_size + within) * D + ch * 8;
         }
         ns_cp_async16(NsTile<D>::at(ks, row, ch * 8), k_cache + off, valid);
         ns_cp_async16(NsTile<D>::at(vs, row, ch * 8), v_cache + off, valid);

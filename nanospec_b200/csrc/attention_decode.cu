@@ -91,14 +91,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     for (int t = 0; t < n_tiles; ++t) {
         __nv_bfloat16* ks = kv + (size_t)(t % kStages) * 2 * kTileKeys * S;
         __nv_bfloat16* vs = ks + kTileKeys * S;
-        ns_cp_async_wait<kStages - 2>();  // tile t has landed
-        __syncthreads();                  // ... for every thread, and every warp is done with tile t-1
-        if (t + kStages - 1 < n_tiles) {  // refill the stage that tile t-1 used
+        __syncthreads();                  // every warp is done with tile t-1: its stage may be refilled
+        if (t + kStages - 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + kStages - 1) % kStages) * 2 * kTileKeys * S;
             load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + kStages - 1) * kTileKeys, kstart, k1, hk,
                             nkv, page_size, page_shift);
         }
         ns_cp_async_commit();
+        ns_cp_async_wait<kStages - 1>();  // tile t has landed; the two after it stay in flight
+        __syncthreads();                  // ... for every thread
         if (t == 0) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk)
