@@ -19,6 +19,12 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
                                              int hk, int nkv, int page_size, int page_shift) {
     constexpr int kChunks = D / 8;
     constexpr int kItems = (kTileKeys * kChunks + THREADS - 1) / THREADS;  // 16-byte pieces per thread and tensor
+    // When the threads divide evenly over the pieces of a row, a thread keeps the same piece of
+    // the row for every item and its rows advance by a constant: no division per item.
+    constexpr bool kRegular = THREADS % kChunks == 0;
+    constexpr int kRowStep = kRegular ? THREADS / kChunks : 0;
+    const int ch0 = kRegular ? threadIdx.x % kChunks : 0;
+    const int row0 = kRegular ? threadIdx.x / kChunks : 0;
     // first the block-table entries of all of this thread's rows (independent loads), then the copies:
     // the copies are ordered against other memory operations, and a table lookup between two of them
     // would cost a full load latency each time
@@ -26,7 +32,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
 #pragma unroll
     for (int i = 0; i < kItems; ++i) {
         const int c = threadIdx.x + i * THREADS;
-        const int key = key0 + c / kChunks;
+        const int row = kRegular ? row0 + i * kRowStep : c / kChunks;
+        const int key = key0 + row;
         const bool valid = c < kTileKeys * kChunks && key >= key_lo && key < key_end;
         // page_shift >= 0: the page size is a power of two (no integer division per row)
         page[i] = valid ? __ldg(bt + (page_shift >= 0 ? key >> page_shift : key / page_size)) : -1;
@@ -35,7 +42,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
     for (int i = 0; i < kItems; ++i) {
         const int c = threadIdx.x + i * THREADS;
         if (c >= kTileKeys * kChunks) break;
-        const int row = c / kChunks, ch = c - row * kChunks;
+        const int row = kRegular ? row0 + i * kRowStep : c / kChunks;
+        const int ch = kRegular ? ch0 : c - row * kChunks;
         const int key = key0 + row;
         const bool valid = page[i] >= 0;
         size_t off = 0;

@@ -3,7 +3,7 @@
 // processed together so that every key and value is read from HBM once per group.
 //
 // Grid (split, kv head x head tile, token).  A block streams its share of the keys through
-// shared memory with cp.async (three stages of 64 keys), computes scores and the weighted sum on
+// shared memory with cp.async (two stages of 64 keys), computes scores and the weighted sum on
 // the tensor cores (m16n8k16, the group's heads padded to 16 rows), keeps the softmax in fp32
 // (online, base 2), and writes an unnormalised partial result with its running maximum and sum.
 // The block that finishes last for a (token, kv head) - found with an atomic counter - merges
@@ -17,11 +17,11 @@
 
 namespace {
 
-constexpr int kStages = 3;  // key/value tiles in flight per block
+constexpr int kStages = 2;  // key/value tiles in flight per block (the kernel is bound by instructions, not by latency: three blocks per SM matter more than a third stage)
 constexpr int kMaxSplits = 16;
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                         int table_stride, const int* __restrict__ token_req, const int* __restrict__ positions,
@@ -131,7 +131,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
                 const float m_new = fmaxf(m[i], mx[i]);  // finite: key kb is valid for every row
-                corr[i] = exp2f(m[i] - m_new);
+                corr[i] = ns_exp2(m[i] - m_new);
                 m[i] = m_new;
                 l[i] *= corr[i];
             }
@@ -139,16 +139,18 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float p = exp2f(s[nb][j] - m[j >> 1]);
+                    const float p = ns_exp2(s[nb][j] - m[j >> 1]);
                     s[nb][j] = p;
                     l[j >> 1] += p;
                 }
             uint32_t pa[4] = {ns_pack_bf16(s[0][0], s[0][1]), ns_pack_bf16(s[0][2], s[0][3]),
                               ns_pack_bf16(s[1][0], s[1][1]), ns_pack_bf16(s[1][2], s[1][3])};
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // some row's maximum moved
 #pragma unroll
-            for (int nb = 0; nb < D / 8; ++nb) {
-                o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
-                o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+                for (int nb = 0; nb < D / 8; ++nb) {
+                    o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
+                    o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+                }
             }
 #pragma unroll
             for (int nb2 = 0; nb2 < D / 16; ++nb2) {
@@ -198,7 +200,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (mt > -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(sm[w * 16 + row] - mt);
+                const float f = ns_exp2(sm[w * 16 + row] - mt);
                 acc += so[((size_t)w * 16 + row) * D + col] * f;
                 lt += sm[64 + w * 16 + row] * f;
             }
@@ -248,7 +250,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         float acc = 0.f, lt = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < kMaxSplits; ++s2) {
-            const float f = ms[s2] == -INFINITY ? 0.f : exp2f(ms[s2] - mt);  // an empty split adds nothing
+            const float f = ms[s2] == -INFINITY ? 0.f : ns_exp2(ms[s2] - mt);  // an empty split adds nothing
             acc += os[s2] * f;
             lt += ls[s2] * f;
         }

@@ -142,7 +142,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
                 const float m_new = fmaxf(m[i], mx[i]);
                 m_use[i] = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
-                corr[i] = exp2f(m[i] - m_use[i]);
+                corr[i] = ns_exp2(m[i] - m_use[i]);
                 m[i] = m_new;
                 l[i] *= corr[i];
             }
@@ -150,14 +150,16 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float p = exp2f(s[nb][j] - m_use[j >> 1]);
+                    const float p = ns_exp2(s[nb][j] - m_use[j >> 1]);
                     s[nb][j] = p;
                     l[j >> 1] += p;
                 }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // some row's maximum moved
 #pragma unroll
-            for (int nb = 0; nb < D / 8; ++nb) {
-                o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
-                o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+                for (int nb = 0; nb < D / 8; ++nb) {
+                    o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
+                    o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+                }
             }
 #pragma unroll
             for (int kb16 = 0; kb16 < 4; ++kb16) {

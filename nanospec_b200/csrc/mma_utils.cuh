@@ -40,6 +40,13 @@ __device__ __forceinline__ void ns_mma_bf16(float (&d)[4], const uint32_t (&a)[4
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x for x <= 0 in one instruction (ex2.approx, about 2 ulp): the softmax weights of the tensor-core kernels
+__device__ __forceinline__ float ns_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t ns_pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
