@@ -25,6 +25,7 @@ class EngineConfig:
     admission: str = "reserve"           # "reserve": worst-case page reservation, never preempts;
                                          # "optimistic": admit on current need, preempt the newest when pages run out
     graph_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    lookahead: bool = True               # launch the next decode step before the last one's tokens reach the host
 
     def __post_init__(self) -> None:
         if self.num_blocks <= 0 or self.block_size <= 0:

@@ -17,11 +17,11 @@
 
 namespace {
 
-constexpr int kStages = 2;  // key/value tiles in flight per block (the kernel is bound by instructions, not by latency: three blocks per SM matter more than a third stage)
 constexpr int kMaxSplits = 16;
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 3)
+// kStages key/value tiles in flight per block: 2 (three blocks per SM) or 3 (two blocks per SM)
+template <int D, int kStages>
+__global__ void __launch_bounds__(kThreads, kStages == 2 ? 3 : 2)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                         int table_stride, const int* __restrict__ token_req, const int* __restrict__ positions,
@@ -258,8 +258,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     }
 }
 
-template <int D>
-int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+template <int D, int kStages>
+int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
                   int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
@@ -269,12 +269,12 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
     const size_t smem = tiles > 16 * S * sizeof(__nv_bfloat16) + scratch ? tiles : 16 * S * sizeof(__nv_bfloat16) + scratch;
     static bool configured = false;
     if (!configured) {
-        NS_CUDA(cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NS_CUDA(cudaFuncSetAttribute(attention_decode_kernel<D, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     const int G = nq / nkv, head_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * head_tiles, n_tokens);
-    NS_LAUNCH((attention_decode_kernel<D>), grid, kThreads, smem, stream, 
+    NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
         nkv, page_size, scale, window, n_splits, head_tiles);
@@ -282,7 +282,30 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
     return NS_OK;
 }
 
+int g_decode_stages = 3;
+
+template <int D>
+int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+                  int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
+                  int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    if (g_decode_stages == 2)
+        return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
+                                          qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
+                                          page_size, scale, window, n_splits, stream);
+    return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
+                                      qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
+                                      page_size, scale, window, n_splits, stream);
+}
+
 }  // namespace
+
+// Pipeline depth of the decode kernel: 3 stages and two blocks per SM (default) or 2 stages and three.
+NS_API int ns_attention_decode_stages(int stages) {
+    if (stages != 2 && stages != 3) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode_stages: %d (2 or 3)", stages);
+    g_decode_stages = stages;
+    return NS_OK;
+}
 
 // Scratch sizes for a launch: floats of part_o, floats of part_ml, ints of counters.
 NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int n_splits, long long* part_o_floats,

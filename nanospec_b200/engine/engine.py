@@ -39,7 +39,7 @@ class Engine:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.runner, config.graph_buckets, config.record_logits)
-        self._pinned_out: torch.Tensor | None = None
+        self._inflight = None  # a decode step that has been launched and not yet read
         self.d2h_bytes_last = 0
 
     # ---- profiling (CUDA events per phase, read once per step) -------------------------------
@@ -89,19 +89,63 @@ class Engine:
 
     # ---- one step ---------------------------------------------------------------------------
     def step(self) -> list[Request]:
-        """Composes a batch, runs it, samples; returns the requests that finished."""
-        batch = self.sched.next_batch()
-        if not batch:
-            return []
-        self._mark("start")
+        """Composes a batch, runs it, samples; returns the requests that finished.
+
+        Decode-only batches go through CUDA graphs.  While nothing else is waiting, the step after
+        such a batch is launched before this one's tokens have reached the host: it takes them on
+        the device, and the host's work (and the graph's launch latency) overlaps the GPU.  A request
+        that turns out to have ended meanwhile simply ignores the extra step's result."""
+        if self._inflight is None:
+            batch = self.sched.next_batch()
+            if not batch:
+                return []
+            self._mark("start")
+            if self.graphs is None or not self.graphs.can_run(batch):
+                return self._run_eager(batch)
+            self._inflight = self._launch_decode(batch, ids_from_device=False)
+        flight = self._inflight
+        ahead = None
+        if self._can_look_ahead(flight.batch):
+            ahead = self._launch_decode([Scheduled(s.req, [0], True) for s in flight.batch], ids_from_device=True)
+        tok, lpr, lpp, raw = self.graphs.collect(flight)
+        self._mark("score")
+        finished = []
+        for row, s in enumerate(flight.batch):
+            req = s.req
+            if req.state != "running":
+                continue  # it ended in the step before; this step ran for it in vain
+            if raw is not None:
+                req.step_logits.append(raw[row])
+            if self._emit(req, TokenInfo(tok[row], lpr[row], lpp[row])):
+                self.sched.finish(req)
+                finished.append(req)
+        self._inflight = ahead
+        self._after_step()
+        return finished
+
+    def _launch_decode(self, batch: list[Scheduled], ids_from_device: bool):
+        flight = self.graphs.launch(batch, self._uniforms(batch), ids_from_device)
+        for s in batch:
+            s.req.committed += 1
+        return flight
+
+    def _can_look_ahead(self, batch: list[Scheduled]) -> bool:
+        if not self.config.lookahead or self.config.record_logits or self.sched.waiting:
+            return False
+        for s in batch:
+            req = s.req
+            # still running after the step in flight, and room for one more position
+            if req.state != "running" or len(req.out_tokens) + 2 > req.params.max_tokens \
+                    or req.committed + 1 > self.runner.max_positions or not self.cache.can_extend(req.id, 1):
+                return False
+        return True
+
+    def _run_eager(self, batch: list[Scheduled]) -> list[Request]:
         sampling = [s for s in batch if s.samples]
-        if self.graphs is not None and self.graphs.can_run(batch):
-            tok, lpr, lpp, raw = self.graphs.run(batch, self._uniforms(sampling))
-        else:
-            entries = [StepEntry(s.req.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
-            hidden = self.runner.run(entries)
-            self._mark("forward")
-            tok, lpr, lpp, raw = self._score(hidden, sampling)
+        entries = [StepEntry(s.req.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
+        hidden = self.runner.run(entries)
+        self._mark("forward")
+        tok, lpr, lpp, raw = self._score(hidden, sampling)
         self._mark("score")
         finished = []
         row = 0
@@ -117,11 +161,14 @@ class Engine:
             if done:
                 self.sched.finish(req)
                 finished.append(req)
+        self._after_step()
+        return finished
+
+    def _after_step(self) -> None:
         self.steps += 1
         if self.steps % 64 == 0:
             ops.check_kernel_errors(self.device)  # a timed-out wait inside a kernel must not pass silently
         self._flush_prof()
-        return finished
 
     def _uniforms(self, sampling: list[Scheduled]) -> list[float]:
         # one uniform per sampled token from the request's own generator (engine/engine.py:283 in

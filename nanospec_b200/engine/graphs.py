@@ -34,7 +34,7 @@ class _Bucket:
         self.size, self.width = size, table_width
         m = runner.manager
         n_groups = len(m.groups)
-        names = ["ids", "positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
+        names = ["positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
                  "temperature", "top_p", "u"]
         self.off: dict[str, int] = {}
         total = 0
@@ -50,11 +50,17 @@ class _Bucket:
         self.host_np = self.host.numpy()
         self.host_f32 = self.host.view(torch.float32).numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        # token ids live apart from the rest: a step launched ahead of its predecessor's results takes
+        # them on the device, from the predecessor's sampled tokens
+        self.ids_host = torch.full((size,), -1, dtype=torch.int32).pin_memory()
+        self.ids_dev = torch.full((size,), -1, dtype=torch.int32, device=runner.device)
         self.row_sig: list[tuple | None] = [None] * size
         self.copied = torch.cuda.Event()
         self.out_token = torch.zeros(size, dtype=torch.int32, device=runner.device)
         self.out_lp = torch.zeros(2, size, dtype=torch.float32, device=runner.device)
-        self.out_host = torch.zeros(3, size, dtype=torch.float32).pin_memory()
+        self.out_host = [torch.zeros(3, size, dtype=torch.float32).pin_memory() for _ in range(2)]  # used in turn
+        self.out_done = [torch.cuda.Event(), torch.cuda.Event()]
+        self.turn = 0
         self.logits = torch.zeros(size, runner.model.vocab_size, dtype=torch.float32, device=runner.device)
         self.sample_scratch = torch.zeros(size * 48, dtype=torch.float32, device=runner.device)
         self.graph: torch.cuda.CUDAGraph | None = None
@@ -71,7 +77,7 @@ class _Bucket:
         tables = [self.dev[o: o + size * table_width].view(size, table_width) for o in self.table_off]
         self.ctx = StepContext(
             n_tokens=size, n_requests=size,
-            token_ids=view("ids", size), positions=view("positions", size), token_req=view("token_req", size),
+            token_ids=self.ids_dev, positions=view("positions", size), token_req=view("token_req", size),
             qo_indptr=view("qo_indptr", size + 1), kv_len=view("kv_len", size), state_slot=view("slots", size),
             q_lens=[1] * size, kv_lens=[table_width * runner.block_size] * size,
             lanes=runner.storage.lane_views(tables), workspace=workspace, dtype=runner.dtype, device=runner.device,
@@ -85,7 +91,7 @@ class _Bucket:
 
     def _fill_padding(self, first: int) -> None:
         o, n = self.off, self.size
-        self.host_np[o["ids"] + first: o["ids"] + n] = -1
+        self.ids_host[first:] = -1
         self.host_np[o["token_req"] + first: o["token_req"] + n] = -1
         self.host_np[o["positions"] + first: o["positions"] + n] = 0
         self.host_np[o["kv_len"] + first: o["kv_len"] + n] = 0
@@ -150,18 +156,23 @@ class DecodeGraphs:
         return self.buckets[size]
 
     def run(self, batch: list[Scheduled], uniforms: list[float]):
-        """Reserves pages, fills the bucket's description, copies it, replays, reads the tokens.
-        Returns (tokens, raw log-probs, processed log-probs, logits rows or None)."""
+        """launch() and collect() in one: (tokens, raw log-probs, processed log-probs, logits rows or None)."""
+        return self.collect(self.launch(batch, uniforms))
+
+    def launch(self, batch: list[Scheduled], uniforms: list[float], ids_from_device: bool = False) -> "InFlight":
+        """Reserves pages, fills the bucket's description, copies it and replays the graph; does not
+        wait.  With `ids_from_device` the step's token ids are the tokens that the bucket's previous
+        replay sampled (same requests in the same rows): the step can be launched before those tokens
+        have reached the host."""
         runner = self.runner
         m = runner.manager
         B = len(batch)
         bk = self._bucket(self.bucket_size(B))
-        entries = [StepEntry(s.req.id, s.tokens, [0]) for s in batch]
+        entries = [StepEntry(s.req.id, [0] if ids_from_device else s.tokens, [0]) for s in batch]
         starts = [m.seq_len[e.req_id] for e in entries]
         runner._reserve(entries)
-        bk.copied.synchronize()  # the previous copy out of the pinned buffer has finished
+        bk.copied.synchronize()  # the previous copy out of the pinned buffers has finished
         o, hn, hf = bk.off, bk.host_np, bk.host_f32
-        hn[o["ids"]: o["ids"] + B] = [s.tokens[0] for s in batch]
         hn[o["positions"]: o["positions"] + B] = starts
         hn[o["token_req"]: o["token_req"] + B] = np.arange(B, dtype=np.int32)
         hn[o["kv_len"]: o["kv_len"] + B] = [st + 1 for st in starts]
@@ -181,23 +192,46 @@ class DecodeGraphs:
                     continue  # this row already holds this request's table
                 hn[toff + r * W: toff + r * W + len(pages)] = pages
                 bk.row_sig[r] = sig if cacheable else None
+        t0 = t1 = None
         if self.timing is not None:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
+        if ids_from_device:
+            bk.ids_dev[:B].copy_(bk.out_token[:B])  # rows beyond B still hold the padding id of the launch before
+        else:
+            bk.ids_host[:B] = torch.tensor([s.tokens[0] for s in batch], dtype=torch.int32)
+            bk.ids_dev.copy_(bk.ids_host, non_blocking=True)
         bk.dev.copy_(bk.host, non_blocking=True)
         bk.copied.record()
-        runner.h2d_bytes_last = bk.total * 4
+        runner.h2d_bytes_last = bk.total * 4 + (0 if ids_from_device else bk.size * 4)
         runner.storage.zero_state_slots(m.take_fresh_slots())
         bk.graph.replay()
         self.replays += 1
-        bk.out_host[0, :B].copy_(bk.out_token[:B], non_blocking=True)
-        bk.out_host[1:, :B].copy_(bk.out_lp[:, :B], non_blocking=True)
+        turn = bk.turn
+        bk.turn ^= 1
+        out_host = bk.out_host[turn]
+        out_host[0, :B].copy_(bk.out_token[:B], non_blocking=True)
+        out_host[1:, :B].copy_(bk.out_lp[:, :B], non_blocking=True)
         raw = bk.logits[:B].cpu() if self.record_logits else None
-        if self.timing is not None:
+        bk.out_done[turn].record()
+        if t1 is not None:
             t1.record()
             self.timing.append((t0, t1))
-        torch.cuda.current_stream().synchronize()
         for e in entries:
             m.trim(e.req_id)
-        tok = [int(x) for x in bk.out_host[0, :B].tolist()]
-        return tok, bk.out_host[1, :B].tolist(), bk.out_host[2, :B].tolist(), raw
+        return InFlight(batch, bk, turn, B, raw)
+
+    def collect(self, flight: "InFlight"):
+        """Waits for a launched step's results: (tokens, raw log-probs, processed log-probs, logits or None)."""
+        bk, B = flight.bucket, flight.n
+        bk.out_done[flight.turn].synchronize()
+        out = bk.out_host[flight.turn]
+        tok = [int(x) for x in out[0, :B].tolist()]
+        return tok, out[1, :B].tolist(), out[2, :B].tolist(), flight.raw
+
+
+class InFlight:
+    """A decode step that has been launched and whose results have not been read yet."""
+
+    def __init__(self, batch: list[Scheduled], bucket: _Bucket, turn: int, n: int, raw) -> None:
+        self.batch, self.bucket, self.turn, self.n, self.raw = batch, bucket, turn, n, raw

@@ -287,7 +287,7 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
 
 
 TILE_Q = 128         # query rows per block of the prefill kernel
-_TARGET_BLOCKS = 222  # decode attention wants about one and a half blocks per SM of a B200 before it splits keys
+_TARGET_BLOCKS = 296  # decode attention wants about two blocks per SM of a B200 before it splits keys further
 
 
 def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
