@@ -152,8 +152,12 @@ def time_decode(eng, batch: int, steps: int, warmup: int) -> tuple[float, float,
         eng.step()          # host ids -> pinned -> device, graph replay, sampled tokens back to the host
     torch.cuda.synchronize()
     host_s = time.perf_counter() - t0
-    assert len(eng.graphs.timing) == steps, "a timed step did not go through the decode graph"
-    dev_ms = sum(s.elapsed_time(e) for s, e in eng.graphs.timing) / steps
+    # every decode step is one graph launch with its own pair of events; steps may be launched one
+    # ahead of their predecessor's results, so the launches inside the timed calls can differ from
+    # the calls by one
+    launched = len(eng.graphs.timing)
+    assert abs(launched - steps) <= 1, f"{launched} graph launches in {steps} timed steps"
+    dev_ms = sum(s.elapsed_time(e) for s, e in eng.graphs.timing) / launched
     eng.graphs.timing = None
     launches = lib.launch_count() - launches0
     if eng.graphs:
