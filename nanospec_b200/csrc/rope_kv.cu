@@ -42,11 +42,67 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
         if (!is_v && j < rot_pairs) {
             float s, c;
             sincosf((float)pos * inv_freq[j], &s, &c);
-            o1 = x1 * c - x2 * s;
-            o2 = x2 * c + x1 * s;
+            // spelled out so that both kernels of this file round alike
+            o1 = __fmaf_rn(x1, c, -__fmul_rn(x2, s));
+            o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
         }
         ns_st(dst, j, o1);
         ns_st(dst, j + half, o2);
+    }
+}
+
+// The same work with one block per token (all heads), for steps with many tokens: a block per
+// (token, head) would then be bound by the rate at which blocks can be scheduled.  cos and sin of
+// the token's angles are computed once and shared through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_req,
+                           const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
+                           T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d,
+                           int rot_pairs, int write_kv) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    extern __shared__ float cs[];  // [rot_pairs] cos, then [rot_pairs] sin
+    const int n = blockIdx.x;
+    const int req = token_req[n];
+    if (req < 0) return;
+    const int pos = positions[n];
+    const int half = d / 2;
+    for (int j = threadIdx.x; j < rot_pairs; j += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[j], &s, &c);
+        cs[j] = c;
+        cs[rot_pairs + j] = s;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)n * (nq + 2 * nkv) * d;
+    size_t base = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)req * table_stride + pos / page_size];
+        base = ((size_t)page * nkv * page_size + pos % page_size) * d;  // cache[page, 0, offset, :]
+    }
+    const size_t head_stride = (size_t)page_size * d;                   // from one kv head to the next
+    const int rot_heads = write_kv ? nq + nkv : nq;
+    for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        T* x = row + (size_t)h * d;
+        const float x1 = ns_ld(x, j), x2 = ns_ld(x, j + half);
+        float o1 = x1, o2 = x2;
+        if (j < rot_pairs) {
+            const float c = cs[j], s = cs[rot_pairs + j];
+            o1 = __fmaf_rn(x1, c, -__fmul_rn(x2, s));
+            o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
+        }
+        T* dst = h < nq ? x : k_cache + base + (size_t)(h - nq) * head_stride;
+        ns_st(dst, j, o1);
+        ns_st(dst, j + half, o2);
+    }
+    if (write_kv) {
+        const T* v = row + (size_t)(nq + nkv) * d;
+        for (int i = threadIdx.x; i < nkv * d; i += blockDim.x) {
+            const int hk = i / d, e = i - hk * d;
+            v_cache[base + (size_t)hk * head_stride + e] = v[i];
+        }
     }
 }
 
@@ -61,6 +117,21 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
     if (d % 2 || rot_pairs > d / 2 || rot_pairs < 0)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_rope_kv_write: head_dim=%d rot_pairs=%d (head_dim must be even, pairs <= head_dim/2)", d, rot_pairs);
     if (nq + 2 * nkv > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_rope_kv_write: %d heads exceed the grid", nq + 2 * nkv);
+    if (n_tokens >= 64 && 2 * (size_t)rot_pairs * sizeof(float) <= 48 * 1024) {
+        const size_t smem = 2 * (size_t)rot_pairs * sizeof(float);
+        if (dtype == NS_F32)
+            NS_LAUNCH((rope_kv_write_token_kernel<float>), n_tokens, 256, smem, stream, (float*)qkv, positions, token_req,
+                      block_table, table_stride, inv_freq, (float*)k_cache, (float*)v_cache, page_size, nq, nkv, d,
+                      rot_pairs, write_kv);
+        else if (dtype == NS_BF16)
+            NS_LAUNCH((rope_kv_write_token_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (__nv_bfloat16*)qkv,
+                      positions, token_req, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache,
+                      (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, rot_pairs, write_kv);
+        else
+            NS_FAIL(NS_ERR_ARGUMENT, "ns_rope_kv_write: unknown dtype %d", dtype);
+        NS_CHECK_LAUNCH("ns_rope_kv_write");
+        return NS_OK;
+    }
     const dim3 grid(n_tokens, nq + 2 * nkv);
     const int threads = d / 2 <= 32 ? 32 : (d / 2 <= 64 ? 64 : 128);
     if (dtype == NS_F32)

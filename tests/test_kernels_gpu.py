@@ -121,16 +121,17 @@ def paged(k: torch.Tensor, v: torch.Tensor, page: int, n_pages: int, seed: int):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("lens", [[7, 12], [90, 33]])  # few tokens: a block per (token, head); many: a block per token
 @pytest.mark.parametrize("nq,nkv,d,page", [(6, 3, 16, 4), (8, 2, 64, 16), (5, 5, 48, 8), (4, 1, 128, 16)])
-def test_rope_kv_write(dtype, nq, nkv, d, page):
+def test_rope_kv_write(dtype, nq, nkv, d, page, lens):
     g = torch.Generator().manual_seed(d)
-    n_pages = 160
+    n_pages = 240
     scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
     inv = plain.plain_inv_freq(d, 500000.0, scaling)
     # two requests: one continues at a late position (large angles), one starts at 0
-    starts, lens = [301, 0], [7, 12]
+    starts = [301, 0]
     perm = torch.randperm(n_pages, generator=g).to(torch.int32)
-    tables_big = torch.stack([perm[:80], perm[80:]])  # disjoint, scattered pages for every logical block
+    tables_big = torch.stack([perm[:120], perm[120:]])  # disjoint, scattered pages for every logical block
     positions, token_req = [], []
     for r, (s, n) in enumerate(zip(starts, lens)):
         positions += list(range(s, s + n))
