@@ -372,3 +372,4 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     if plan["tiles"] is not None:
         attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"])
     return out
+
