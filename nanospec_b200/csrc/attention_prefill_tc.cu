@@ -1,0 +1,320 @@
+// Prefill attention on the 5th-generation tensor cores (head size 128, bfloat16): portions of
+// prompts, causal by absolute position, keys and values read from the paged cache.
+//
+// One block = 128 consecutive query tokens of one request and one query head.  Per 64 keys:
+//   S = Q K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA), S in TMEM
+//   softmax          128 threads, one query row each (the row of S is read with tcgen05.ld, so the
+//                    running maximum and sum need no exchange between threads), fp32, base 2;
+//                    the weights go to shared memory as bf16, the accumulator O in TMEM is
+//                    rescaled only when some row's maximum moved
+//   O += P V         tcgen05.mma, P from shared memory, V as it lies in the cache (dim contiguous:
+//                    an MN-major operand)
+// Warp roles: warp 0 (one lane) issues the TMA loads - the keys of a block come from 64/page_size
+// cache pages, found through the request's block table; warp 1 (one lane) issues the MMAs and
+// owns the TMEM allocation; warps 2-5 are the softmax threads and write the output.  S is double
+// buffered in TMEM, so the scores of block j+1 are computed while block j is in the softmax.
+//
+// Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
+// block winds down.  Head sizes other than 128, page sizes other than 8/16/32/64 and windows
+// are served by the m16n8k16 kernel of attention_prefill.cu.
+#include "tcgen05_utils.cuh"
+
+namespace {
+
+constexpr int kBQ = 128;       // query rows per block = UMMA M
+constexpr int kBK = 64;        // keys per block
+constexpr int kD = 128;        // head size
+constexpr int kKvStages = 3;
+constexpr int kTcThreads = 192;
+constexpr float kLog2eTc = 1.4426950408889634f;
+
+constexpr int kQBytes = kBQ * kD * 2;          // 32 KB: two halves of 128 rows x 128 B
+constexpr int kKBytes = kBK * kD * 2;          // 16 KB: two halves of 64 rows x 128 B
+constexpr int kPBytes = kBQ * kBK * 2;         // 16 KB: 128 rows x 128 B
+constexpr int kSmemTc = kQBytes + kKvStages * 2 * kKBytes + 2 * kPBytes + 1024 + 256;
+constexpr int kTmemColsTc = 256;               // S0 [0,64), S1 [64,128), O [128,256)
+
+enum TcAttnError { kErrAttnLoader = 11, kErrAttnMma = 12, kErrAttnSoftmax = 13 };
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// instruction descriptors: D fp32, A and B bf16; B K-major (scores) or MN-major (values)
+__device__ __forceinline__ constexpr uint32_t idesc_tc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(kBQ >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                            int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
+                            const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
+                            int page_size, float scale, int* __restrict__ error_flag) {
+    ns_pdl_launch_dependents();
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t q_smem = base;
+    const uint32_t kv_smem = q_smem + kQBytes;                      // [stage][K | V]
+    const uint32_t p_smem = kv_smem + kKvStages * 2 * kKBytes;      // [2]
+    const uint32_t bar0 = p_smem + 2 * kPBytes;
+    // barriers
+    const uint32_t q_full = bar0;
+    auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
+    auto s_full = [&](int b) { return bar0 + 8u * (1 + 2 * kKvStages + b); };
+    auto s_free = [&](int b) { return bar0 + 8u * (3 + 2 * kKvStages + b); };
+    auto p_ready = [&](int b) { return bar0 + 8u * (5 + 2 * kKvStages + b); };
+    const uint32_t o_done = bar0 + 8u * (7 + 2 * kKvStages);
+    const uint32_t holder = o_done + 8u;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int req = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y;
+    const int hk = h / (nq / nkv);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full(b), 1);
+            mbar_init(s_free(b), 128);
+            mbar_init(p_ready(b), 128);
+        }
+        mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) tmem_alloc(holder, kTmemColsTc);
+    ns_pdl_wait();  // everything below reads what earlier kernels wrote (q, the cache, the step's description)
+    const int tok0 = qo_indptr[req] + q_off;
+    const int rows = min(kBQ, qo_indptr[req + 1] - tok0);
+    const int pos0 = positions[tok0];
+    const int kend = pos0 + rows;                         // keys 0 .. kend-1 are seen by the last row
+    const int n_blocks = (kend + kBK - 1) / kBK;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
+    const uint32_t tmem_s[2] = {tmem_base, tmem_base + 64u};
+    const uint32_t tmem_o = tmem_base + 128u;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- loader ----------------
+        mbar_expect_tx(q_full, kQBytes);
+        tma_load_2d(q_smem, &map_q, h * kD, tok0, q_full);
+        tma_load_2d(q_smem + kBQ * 128, &map_q, h * kD + 64, tok0, q_full);
+        const int* bt = block_table + (size_t)req * table_stride;
+        const int last_blk = (kend - 1) / page_size;      // the last page that holds one of the request's keys
+        const int pages_per_block = kBK / page_size;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int s = j % kKvStages;
+            if (!mbar_wait(kv_empty(s), ((uint32_t)(j / kKvStages) & 1u) ^ 1u)) { atomicExch(error_flag, kErrAttnLoader); break; }
+            mbar_expect_tx(kv_full(s), 2 * kKBytes);
+            const uint32_t k_dst = kv_smem + s * 2 * kKBytes, v_dst = k_dst + kKBytes;
+            for (int i = 0; i < pages_per_block; ++i) {
+                // pages past the request's end repeat its last page: finite values that the mask hides
+                const int blk = min(j * pages_per_block + i, last_blk);
+                const int row = (bt[blk] * nkv + hk) * page_size;
+                const uint32_t off = (uint32_t)(i * page_size) * 128u;
+                tma_load_2d(k_dst + off, &map_k, 0, row, kv_full(s));
+                tma_load_2d(k_dst + kBK * 128 + off, &map_k, 64, row, kv_full(s));
+                tma_load_2d(v_dst + off, &map_v, 0, row, kv_full(s));
+                tma_load_2d(v_dst + kBK * 128 + off, &map_v, 64, row, kv_full(s));
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc_s = idesc_tc(kBK, false);
+        constexpr uint32_t idesc_o = idesc_tc(kD, true);
+        bool ok = mbar_wait(q_full, 0);
+        auto issue_scores = [&](int j) -> bool {
+            const int s = j % kKvStages, b = j & 1;
+            if (!mbar_wait(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
+            if (!mbar_wait(s_free(b), ((uint32_t)(j >> 1) & 1u) ^ 1u)) return false;
+            tc_fence_after();
+            const uint32_t k_src = kv_smem + s * 2 * kKBytes;
+#pragma unroll
+            for (int kk = 0; kk < kD / 16; ++kk) {
+                const uint32_t qa = q_smem + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
+                const uint32_t kb = k_src + (kk >> 2) * (kBK * 128) + (kk & 3) * 32;
+                umma_bf16(tmem_s[b], smem_desc(qa), smem_desc(kb), idesc_s, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full(b));
+            return true;
+        };
+        if (ok && n_blocks > 0) ok = issue_scores(0);
+        for (int j = 0; ok && j < n_blocks; ++j) {
+            if (j + 1 < n_blocks) ok = issue_scores(j + 1);  // the next block's scores run under this block's softmax
+            if (!ok) break;
+            const int s = j % kKvStages, b = j & 1;
+            if (!mbar_wait(p_ready(b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t v_src = kv_smem + s * 2 * kKBytes + kKBytes;
+            const uint32_t p_src = p_smem + b * kPBytes;
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)
+                umma_bf16(tmem_o, smem_desc(p_src + kk * 32), smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024), idesc_o,
+                          (j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(kv_empty(s));  // the stage's keys and values have been read
+            umma_commit(o_done);       // the accumulator holds blocks 0..j
+        }
+        if (!ok) atomicExch(error_flag, kErrAttnMma);
+    } else if (warp >= 2) {
+        // ---------------- softmax and output: one query row per thread ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                       // TMEM lane = query row of the tile
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int pos_row = pos0 + min(row, rows - 1);
+        const float sl = scale * kLog2eTc;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int b = j & 1;
+            if (lane == 0) ok = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sv[2][32];
+            tmem_ld32(tmem_s[b] + lane_addr, sv[0]);
+            tmem_ld32(tmem_s[b] + lane_addr + 32, sv[1]);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(s_free(b));                                 // the scores are in registers
+            const int key0 = j * kBK;
+            const bool masked = key0 + kBK - 1 > pos0;              // some row of the tile does not see the whole block
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kBK; ++c) {
+                float x = __uint_as_float(sv[c >> 5][c & 31]) * sl;
+                if (masked && key0 + c > pos_row) x = -INFINITY;
+                sv[c >> 5][c & 31] = __float_as_uint(x);
+                mx = fmaxf(mx, x);
+            }
+            const float m_new = fmaxf(m, mx);                       // block 0 holds key 0: finite from the start
+            const float corr = ex2(m - m_new);
+            float sum = 0.f;
+            // weights as bf16 into this row of the P tile: 8 pieces of 16 bytes, 128-byte swizzle
+            const uint32_t p_row = p_smem + b * kPBytes + (uint32_t)row * 128u;
+#pragma unroll
+            for (int c8 = 0; c8 < kBK / 8; ++c8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int c = c8 * 8 + 2 * t;
+                    const float p0 = ex2(__uint_as_float(sv[c >> 5][c & 31]) - m_new);
+                    const float p1 = ex2(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - m_new);
+                    sum += p0 + p1;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                    packed[t] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                const uint32_t dst = p_row + (uint32_t)((c8 ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
+                             "r"(packed[2]), "r"(packed[3]) : "memory");
+            }
+            l = l * corr + sum;
+            if (j > 0) {
+                // the accumulator must hold block j-1 before it is rescaled (and before block j is added)
+                if (lane == 0) ok = mbar_wait(o_done, (uint32_t)(j - 1) & 1u);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, m_new != m)) {          // some row's maximum moved
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kD; c0 += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(tmem_o + lane_addr + c0, ov);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                        tmem_st32(tmem_o + lane_addr + c0, ov);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            m = m_new;
+            fence_async_smem();                                     // the P tile is read by the tensor core
+            tc_fence_before();
+            mbar_arrive(p_ready(b));
+        }
+        if (ok && n_blocks > 0) {
+            if (lane == 0) ok = mbar_wait(o_done, (uint32_t)(n_blocks - 1) & 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        if (!ok) {
+            if (lane == 0) atomicExch(error_flag, kErrAttnSoftmax);
+        } else if (n_blocks > 0) {
+            tc_fence_after();
+            const float inv = 1.f / l;
+            __nv_bfloat16* orow = out + (size_t)(tok0 + row) * o_stride + (size_t)h * kD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + lane_addr + c0, ov);
+                tmem_ld_wait();
+                if (row < rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u;
+                        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            hp[t] = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * t]) * inv, __uint_as_float(ov[i + 2 * t + 1]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c0 + i) = u;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemColsTc);
+    }
+}
+
+}  // namespace
+
+// q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
+// lane's pages [n_pages, nkv, page_size, 128]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of
+// this step, a multiple of 128).  Head size 128 only; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
+NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
+                                   long long n_pages, const int* block_table, int table_stride, const int* positions,
+                                   const int* qo_indptr, const int* tiles, int n_tiles, void* out, int o_stride, int nq,
+                                   int nkv, int d, int page_size, float scale, int* error_flag, cudaStream_t stream) {
+    if (n_tiles <= 0) return NS_OK;
+    if (d != kD) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: head_dim=%d (128 only)", d);
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: page_size=%d (8, 16, 32 or 64)", page_size);
+    if (nkv < 1 || nq % nkv || nq > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads", nq, nkv);
+    if (q_stride % 8 || o_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: rows must be 16-byte aligned");
+    if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: no error flag");
+    CUtensorMap mq, mk, mv;
+    int rc = ns_make_map_bf16(&mq, q, (unsigned long long)n_tokens, nq * kD, q_stride, kBQ, "ns_attention_prefill_tc");
+    if (rc) return rc;
+    const unsigned long long cache_rows = (unsigned long long)n_pages * nkv * page_size;
+    rc = ns_make_map_bf16(&mk, k_cache, cache_rows, kD, kD, page_size, "ns_attention_prefill_tc");
+    if (rc) return rc;
+    rc = ns_make_map_bf16(&mv, v_cache, cache_rows, kD, kD, page_size, "ns_attention_prefill_tc");
+    if (rc) return rc;
+    static bool configured = false;
+    if (!configured) {
+        NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc));
+        configured = true;
+    }
+    NS_LAUNCH((attention_prefill_tc_kernel), dim3(n_tiles, nq), kTcThreads, kSmemTc, stream, mq, mk, mv, block_table,
+              table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale,
+              error_flag);
+    NS_CHECK_LAUNCH("ns_attention_prefill_tc");
+    return NS_OK;
+}

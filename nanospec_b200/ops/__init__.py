@@ -286,7 +286,8 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
                   head_dim, write_kv=True)
 
 
-TILE_Q = 128         # query rows per block of the prefill kernel
+TILE_Q = 128         # query rows per block of the prefill kernels
+USE_TCGEN05_ATTENTION = True
 _TARGET_BLOCKS = 296  # decode attention wants about two blocks per SM of a B200 before it splits keys further
 
 
@@ -318,8 +319,17 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor) -> None:
-    """Tensor-core attention for portions of prompts (csrc/attention_prefill.cu).
-    `tiles`: int32 [n, 2] of (request, offset among its tokens of this step)."""
+    """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
+    among its tokens of this step).  Head size 128 with pages of 8 to 64 tokens and no window runs
+    on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
+    if USE_TCGEN05_ATTENTION and head_dim == 128 and window == 0 and lane.page_size in (8, 16, 32, 64) \
+            and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+        lib.call("ns_attention_prefill_tc", qkv.data_ptr(), qkv.stride(0), qkv.shape[0], lane.k.data_ptr(),
+                 lane.v.data_ptr(), lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0),
+                 ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
+                 out.stride(0), nq, nkv, head_dim, lane.page_size, float(scale), _tc(qkv.device).error.data_ptr(),
+                 _stream())
+        return
     lib.call("ns_attention_prefill", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,

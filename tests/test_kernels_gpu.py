@@ -351,3 +351,29 @@ def test_decode_attention_splits_and_counters(n_req, S):
                 full = plain.plain_attention(q, k, v)
                 torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
         assert int(ctx.workspace.get("attn_counters", 1, 1, torch.int32).sum()) == 0
+
+
+@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 8), (6, 1, 32), (32, 8, 64)])
+def test_tcgen05_prefill_attention(nq, nkv, page):
+    """Head size 128 takes the tcgen05 kernel: prompts from 2 to 1,500 tokens, portions that continue a
+    request, tiles that end inside a page, a far key that every query must find - against the plain
+    attention and against the m16n8k16 kernel."""
+    d = 128
+    requests = [(1500, 1500, 7), (129, 128, 3), (700, 2, 650), (333, 70, 2), (64, 64, 63), (257, 129, 128), (1000, 300, 640)]
+    ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=5000 // page + 40, seed=page)
+    outs = {}
+    for tc in (True, False):
+        ops().USE_TCGEN05_ATTENTION = tc
+        ctx.extras = {}
+        out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+        torch.cuda.synchronize()
+        ops().check_kernel_errors()
+        outs[tc] = out
+    ops().USE_TCGEN05_ATTENTION = True
+    row = 0
+    for (S, q_len, _), (q, k, v, start) in zip(requests, want):
+        full = plain.plain_attention(q, k, v)
+        torch.testing.assert_close(outs[True][row: row + q_len].float().cpu().view(q_len, nq, d), full[start:], rtol=3e-2, atol=3e-2)
+        row += q_len
+    torch.testing.assert_close(outs[True].float(), outs[False].float(), rtol=3e-2, atol=3e-2)
