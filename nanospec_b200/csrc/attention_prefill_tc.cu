@@ -72,8 +72,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t holder = o_done + 8u;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int req = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y;
+    // heads vary fastest: the host lists the tiles with the most keys first, and blocks are
+    // scheduled in that order, so the long tiles do not end up alone at the tail
+    const int req = tiles[2 * blockIdx.y], q_off = tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x;
     const int hk = h / (nq / nkv);
 
     if (threadIdx.x == 0) {
@@ -190,15 +192,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_arrive(s_free(b));                                 // the scores are in registers
             const int key0 = j * kBK;
             const bool masked = key0 + kBK - 1 > pos0;              // some row of the tile does not see the whole block
+            // maximum of the raw scores first (the scale is positive, so it commutes with the maximum),
+            // then each weight is one fused multiply-add and one ex2
             float mx = -INFINITY;
+            if (masked) {
 #pragma unroll
-            for (int c = 0; c < kBK; ++c) {
-                float x = __uint_as_float(sv[c >> 5][c & 31]) * sl;
-                if (masked && key0 + c > pos_row) x = -INFINITY;
-                sv[c >> 5][c & 31] = __float_as_uint(x);
-                mx = fmaxf(mx, x);
+                for (int c = 0; c < kBK; ++c) {
+                    if (key0 + c > pos_row) sv[c >> 5][c & 31] = 0xff800000u;  // -inf
+                    mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBK; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
             }
-            const float m_new = fmaxf(m, mx);                       // block 0 holds key 0: finite from the start
+            const float m_new = fmaxf(m, mx * sl);                  // block 0 holds key 0: finite from the start
             const float corr = ex2(m - m_new);
             float sum = 0.f;
             // weights as bf16 into this row of the P tile: 8 pieces of 16 bytes, 128-byte swizzle
@@ -209,8 +216,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
                     const int c = c8 * 8 + 2 * t;
-                    const float p0 = ex2(__uint_as_float(sv[c >> 5][c & 31]) - m_new);
-                    const float p1 = ex2(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - m_new);
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
                     sum += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     packed[t] = *reinterpret_cast<uint32_t*>(&v);
@@ -295,7 +302,8 @@ NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, co
     if (d != kD) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: head_dim=%d (128 only)", d);
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: page_size=%d (8, 16, 32 or 64)", page_size);
-    if (nkv < 1 || nq % nkv || nq > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads", nq, nkv);
+    if (nkv < 1 || nq % nkv || n_tiles > 65535)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads, %d tiles", nq, nkv, n_tiles);
     if (q_stride % 8 || o_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: rows must be 16-byte aligned");
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: no error flag");
@@ -312,7 +320,7 @@ NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, co
         NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc));
         configured = true;
     }
-    NS_LAUNCH((attention_prefill_tc_kernel), dim3(n_tiles, nq), kTcThreads, kSmemTc, stream, mq, mk, mv, block_table,
+    NS_LAUNCH((attention_prefill_tc_kernel), dim3(nq, n_tiles), kTcThreads, kSmemTc, stream, mq, mk, mv, block_table,
               table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale,
               error_flag);
     NS_CHECK_LAUNCH("ns_attention_prefill_tc");

@@ -349,7 +349,9 @@ def _attention_plan(ctx) -> dict:
             starts.append(row)
             row += n
         decode = [s for s, n in zip(starts, ctx.q_lens) if n == 1]
+        # the tiles that see the most keys come first: blocks are scheduled in this order
         tiles = [(b, off) for b, n in enumerate(ctx.q_lens) if n > 1 for off in range(0, n, TILE_Q)]
+        tiles.sort(key=lambda t: -(ctx.kv_lens[t[0]] - ctx.q_lens[t[0]] + min(t[1] + TILE_Q, ctx.q_lens[t[0]])))
         dev = ctx.device
         plan = {
             "n_decode": len(decode),
