@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, CacheStorage, PoolExhausted
@@ -110,52 +111,51 @@ class ModelRunner:
         if len(set(ids)) != len(ids):
             raise ValueError("a request may appear once in a step")
         vocab = self.model.vocab_size
+        m = self.manager
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        N = sum(q_lens)
+        ids_np = np.empty(N, dtype=np.int64)
+        at = 0
         for e in entries:
-            for t in e.tokens:
-                if not 0 <= t < vocab:
-                    raise ValueError(f"token id {t} of request {e.req_id} is outside the vocabulary of {vocab}")
+            ids_np[at: at + len(e.tokens)] = e.tokens
+            at += len(e.tokens)
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise ValueError(f"request {e.req_id} wants logits at place {w} of {len(e.tokens)} tokens")
-        m = self.manager
+        if N and (ids_np.min() < 0 or ids_np.max() >= vocab):
+            bad = int(ids_np[(ids_np < 0) | (ids_np >= vocab)][0])
+            raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
         starts = [m.seq_len[e.req_id] for e in entries]
         self._reserve(entries)
 
-        B = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
         kv_lens = [s + n for s, n in zip(starts, q_lens)]
-        N = sum(q_lens)
-        token_ids, positions, token_req, qo_indptr, want_rows = [], [], [], [0], []
-        for b, (e, s) in enumerate(zip(entries, starts)):
-            base = qo_indptr[-1]
-            token_ids.extend(e.tokens)
-            positions.extend(range(s, s + len(e.tokens)))
-            token_req.extend([b] * len(e.tokens))
-            qo_indptr.append(base + len(e.tokens))
-            want_rows.extend(base + w for w in e.want)
+        qo_indptr = np.zeros(B + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=qo_indptr[1:])
+        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)]) if N else np.zeros(0, np.int32)
+        token_req = np.repeat(np.arange(B, dtype=np.int32), q_lens)
+        want_rows = [int(qo_indptr[b]) + w for b, e in enumerate(entries) for w in e.want]
         slots = [m.state_slot(e.req_id) for e in entries]
         tables, widths = [], []
         for gi in range(len(m.groups)):
             rows = [m.table(gi, e.req_id) for e in entries]
             width = max(1, max(len(r) for r in rows))
-            flat: list[int] = []
-            for r in rows:
-                flat.extend(r)
-                flat.extend([0] * (width - len(r)))
-            tables.append(flat)
+            table = np.zeros((B, width), dtype=np.int32)
+            for b, r in enumerate(rows):
+                table[b, : len(r)] = r
+            tables.append(table.reshape(-1))
             widths.append(width)
 
-        parts = [token_ids, positions, token_req, qo_indptr, kv_lens, slots, want_rows, *tables]
+        parts = [ids_np.astype(np.int32), positions, token_req, qo_indptr, np.asarray(kv_lens, dtype=np.int32),
+                 np.asarray(slots, dtype=np.int32), np.asarray(want_rows, dtype=np.int32), *tables]
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
             total += len(p) + (-len(p) % 4)  # 16-byte aligned sections
         host, turn = self._staging.get(total)
-        flat_all: list[int] = []
-        for p in parts:
-            flat_all.extend(p)
-            flat_all.extend([0] * (-len(p) % 4))
-        host[:total] = torch.tensor(flat_all, dtype=torch.int32)
+        host_np = host.numpy()
+        for off, p in zip(offsets, parts):
+            host_np[off: off + len(p)] = p
         if self._meta_dev is None or self._meta_dev.numel() < total:
             self._meta_dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
         dev = self._meta_dev
