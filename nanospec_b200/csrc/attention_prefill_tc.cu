@@ -1,7 +1,8 @@
 // Prefill attention on the 5th-generation tensor cores (head size 128, bfloat16): portions of
 // prompts, causal by absolute position, keys and values read from the paged cache.
 //
-// One block = 128 consecutive query tokens of one request and one query head.  Per 64 keys:
+// One block = 256 consecutive query tokens of one request (two tiles of 128, each with its own softmax
+// warpgroup and accumulator; they share every block of keys) and one query head.  Per 64 keys and tile:
 //   S = Q K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA), S in TMEM
 //   softmax          128 threads, one query row each (the row of S is read with tcgen05.ld, so the
 //                    running maximum and sum need no exchange between threads), fp32, base 2;
@@ -11,7 +12,7 @@
 //                    an MN-major operand)
 // Warp roles: warp 0 (one lane) issues the TMA loads - the keys of a block come from 64/page_size
 // cache pages, found through the request's block table; warp 1 (one lane) issues the MMAs and
-// owns the TMEM allocation; warps 2-5 are the softmax threads and write the output.  S is double
+// owns the TMEM allocation; warps 2-5 and 6-9 are the softmax threads of the two tiles and write the output.  S is double
 // buffered in TMEM, so the scores of block j+1 are computed while block j is in the softmax.
 //
 // Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
@@ -21,18 +22,19 @@
 
 namespace {
 
-constexpr int kBQ = 128;       // query rows per block = UMMA M
+constexpr int kBQ = 128;       // query rows per tile = UMMA M
+constexpr int kTiles = 2;      // query tiles per block: they share every key/value block
 constexpr int kBK = 64;        // keys per block
 constexpr int kD = 128;        // head size
-constexpr int kKvStages = 3;
-constexpr int kTcThreads = 192;
+constexpr int kKvStages = 2;
+constexpr int kTcThreads = 64 + kTiles * 128;
 constexpr float kLog2eTc = 1.4426950408889634f;
 
-constexpr int kQBytes = kBQ * kD * 2;          // 32 KB: two halves of 128 rows x 128 B
+constexpr int kQBytes = kBQ * kD * 2;          // 32 KB per tile: two halves of 128 rows x 128 B
 constexpr int kKBytes = kBK * kD * 2;          // 16 KB: two halves of 64 rows x 128 B
 constexpr int kPBytes = kBQ * kBK * 2;         // 16 KB: 128 rows x 128 B
-constexpr int kSmemTc = kQBytes + kKvStages * 2 * kKBytes + 2 * kPBytes + 1024 + 256;
-constexpr int kTmemColsTc = 256;               // S0 [0,64), S1 [64,128), O [128,256)
+constexpr int kSmemTc = kTiles * kQBytes + kKvStages * 2 * kKBytes + kTiles * 2 * kPBytes + 1024 + 256;
+constexpr int kTmemColsTc = 512;               // S[tile][buffer] at (tile * 2 + buffer) * 64, O[tile] at 256 + tile * 128
 
 enum TcAttnError { kErrAttnLoader = 11, kErrAttnMma = 12, kErrAttnSoftmax = 13 };
 
@@ -57,19 +59,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     ns_pdl_launch_dependents();
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t q_smem = base;
-    const uint32_t kv_smem = q_smem + kQBytes;                      // [stage][K | V]
-    const uint32_t p_smem = kv_smem + kKvStages * 2 * kKBytes;      // [2]
-    const uint32_t bar0 = p_smem + 2 * kPBytes;
-    // barriers
+    const uint32_t q_smem = base;                                   // [tile]
+    const uint32_t kv_smem = q_smem + kTiles * kQBytes;             // [stage][K | V]
+    const uint32_t p_smem = kv_smem + kKvStages * 2 * kKBytes;      // [tile][buffer]
+    const uint32_t bar0 = p_smem + kTiles * 2 * kPBytes;
+    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], s_free[2], p_ready[2], o_done
     const uint32_t q_full = bar0;
     auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
-    auto s_full = [&](int b) { return bar0 + 8u * (1 + 2 * kKvStages + b); };
-    auto s_free = [&](int b) { return bar0 + 8u * (3 + 2 * kKvStages + b); };
-    auto p_ready = [&](int b) { return bar0 + 8u * (5 + 2 * kKvStages + b); };
-    const uint32_t o_done = bar0 + 8u * (7 + 2 * kKvStages);
-    const uint32_t holder = o_done + 8u;
+    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 7 + which); };
+    auto s_full = [&](int t, int b) { return tile_bar(t, b); };
+    auto s_free = [&](int t, int b) { return tile_bar(t, 2 + b); };
+    auto p_ready = [&](int t, int b) { return tile_bar(t, 4 + b); };
+    auto o_done = [&](int t) { return tile_bar(t, 6); };
+    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 7);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads vary fastest: the host lists the tiles with the most keys first, and blocks are
@@ -84,37 +87,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(s_full(b), 1);
-            mbar_init(s_free(b), 128);
-            mbar_init(p_ready(b), 128);
+        for (int t = 0; t < kTiles; ++t) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(s_full(t, b), 1);
+                mbar_init(s_free(t, b), 128);
+                mbar_init(p_ready(t, b), 128);
+            }
+            mbar_init(o_done(t), 1);
         }
-        mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
     if (warp == 1) tmem_alloc(holder, kTmemColsTc);
     ns_pdl_wait();  // everything below reads what earlier kernels wrote (q, the cache, the step's description)
     const int tok0 = qo_indptr[req] + q_off;
-    const int rows = min(kBQ, qo_indptr[req + 1] - tok0);
+    const int rows_all = min(kTiles * kBQ, qo_indptr[req + 1] - tok0);
     const int pos0 = positions[tok0];
-    const int kend = pos0 + rows;                         // keys 0 .. kend-1 are seen by the last row
-    const int n_blocks = (kend + kBK - 1) / kBK;
+    // per tile: its valid rows and the number of key blocks its last row sees (0 rows: the tile is idle)
+    int rows_t[kTiles], nblk_t[kTiles];
+    int n_blocks = 0;
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) {
+        rows_t[t] = max(0, min(kBQ, rows_all - t * kBQ));
+        nblk_t[t] = rows_t[t] > 0 ? (pos0 + t * kBQ + rows_t[t] + kBK - 1) / kBK : 0;
+        n_blocks = max(n_blocks, nblk_t[t]);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
-    const uint32_t tmem_s[2] = {tmem_base, tmem_base + 64u};
-    const uint32_t tmem_o = tmem_base + 128u;
+    auto tmem_s = [&](int t, int b) { return tmem_base + (uint32_t)((t * 2 + b) * 64); };
+    auto tmem_o = [&](int t) { return tmem_base + 256u + (uint32_t)(t * 128); };
 
     if (warp == 0 && lane == 0) {
         // ---------------- loader ----------------
-        mbar_expect_tx(q_full, kQBytes);
-        tma_load_2d(q_smem, &map_q, h * kD, tok0, q_full);
-        tma_load_2d(q_smem + kBQ * 128, &map_q, h * kD + 64, tok0, q_full);
+        mbar_expect_tx(q_full, kTiles * kQBytes);
+        for (int t = 0; t < kTiles; ++t) {  // rows past the step's tokens are zero-filled by TMA
+            tma_load_2d(q_smem + t * kQBytes, &map_q, h * kD, tok0 + t * kBQ, q_full);
+            tma_load_2d(q_smem + t * kQBytes + kBQ * 128, &map_q, h * kD + 64, tok0 + t * kBQ, q_full);
+        }
         const int* bt = block_table + (size_t)req * table_stride;
-        const int last_blk = (kend - 1) / page_size;      // the last page that holds one of the request's keys
+        const int last_blk = (pos0 + rows_all - 1) / page_size;  // the last page that holds one of the keys seen here
         const int pages_per_block = kBK / page_size;
         for (int j = 0; j < n_blocks; ++j) {
             const int s = j % kKvStages;
@@ -122,7 +136,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_expect_tx(kv_full(s), 2 * kKBytes);
             const uint32_t k_dst = kv_smem + s * 2 * kKBytes, v_dst = k_dst + kKBytes;
             for (int i = 0; i < pages_per_block; ++i) {
-                // pages past the request's end repeat its last page: finite values that the mask hides
+                // pages past the last key repeat the last page: finite values that the mask hides
                 const int blk = min(j * pages_per_block + i, last_blk);
                 const int row = (bt[blk] * nkv + hk) * page_size;
                 const uint32_t off = (uint32_t)(i * page_size) * 128u;
@@ -137,19 +151,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         constexpr uint32_t idesc_s = idesc_tc(kBK, false);
         constexpr uint32_t idesc_o = idesc_tc(kD, true);
         bool ok = mbar_wait(q_full, 0);
+        // scores of key block j for every tile that sees it
         auto issue_scores = [&](int j) -> bool {
             const int s = j % kKvStages, b = j & 1;
             if (!mbar_wait(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
-            if (!mbar_wait(s_free(b), ((uint32_t)(j >> 1) & 1u) ^ 1u)) return false;
-            tc_fence_after();
             const uint32_t k_src = kv_smem + s * 2 * kKBytes;
+            for (int t = 0; t < kTiles; ++t) {
+                if (j >= nblk_t[t]) continue;
+                if (!mbar_wait(s_free(t, b), ((uint32_t)(j >> 1) & 1u) ^ 1u)) return false;
+                tc_fence_after();
 #pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk) {
-                const uint32_t qa = q_smem + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
-                const uint32_t kb = k_src + (kk >> 2) * (kBK * 128) + (kk & 3) * 32;
-                umma_bf16(tmem_s[b], smem_desc(qa), smem_desc(kb), idesc_s, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t qa = q_smem + t * kQBytes + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
+                    const uint32_t kb = k_src + (kk >> 2) * (kBK * 128) + (kk & 3) * 32;
+                    umma_bf16(tmem_s(t, b), smem_desc(qa), smem_desc(kb), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(t, b));
             }
-            umma_commit(s_full(b));
             return true;
         };
         if (ok && n_blocks > 0) ok = issue_scores(0);
@@ -157,41 +175,47 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (j + 1 < n_blocks) ok = issue_scores(j + 1);  // the next block's scores run under this block's softmax
             if (!ok) break;
             const int s = j % kKvStages, b = j & 1;
-            if (!mbar_wait(p_ready(b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
-            tc_fence_after();
             const uint32_t v_src = kv_smem + s * 2 * kKBytes + kKBytes;
-            const uint32_t p_src = p_smem + b * kPBytes;
+            for (int t = 0; t < kTiles && ok; ++t) {
+                if (j >= nblk_t[t]) continue;
+                if (!mbar_wait(p_ready(t, b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t p_src = p_smem + (t * 2 + b) * kPBytes;
 #pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk)
-                umma_bf16(tmem_o, smem_desc(p_src + kk * 32), smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024), idesc_o,
-                          (j > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(kv_empty(s));  // the stage's keys and values have been read
-            umma_commit(o_done);       // the accumulator holds blocks 0..j
+                for (int kk = 0; kk < kBK / 16; ++kk)
+                    umma_bf16(tmem_o(t), smem_desc(p_src + kk * 32), smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
+                              idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(o_done(t));    // this tile's accumulator holds blocks 0..j
+            }
+            umma_commit(kv_empty(s));      // the stage's keys and values have been read by every tile
         }
         if (!ok) atomicExch(error_flag, kErrAttnMma);
     } else if (warp >= 2) {
-        // ---------------- softmax and output: one query row per thread ----------------
-        const int quarter = warp & 3;
+        // ---------------- softmax and output: one query row per thread, one warpgroup per tile ----------------
+        const int t = (warp - 2) >> 2;                             // the tile this warpgroup serves
+        const int quarter = warp & 3;                              // the TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;                       // TMEM lane = query row of the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int pos_row = pos0 + min(row, rows - 1);
+        const int rows = rows_t[t], my_blocks = nblk_t[t];
+        const int tile_pos0 = pos0 + t * kBQ;
+        const int pos_row = tile_pos0 + min(row, max(rows, 1) - 1);
         const float sl = scale * kLog2eTc;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_blocks; ++j) {
+        for (int j = 0; j < my_blocks; ++j) {
             const int b = j & 1;
-            if (lane == 0) ok = mbar_wait(s_full(b), (uint32_t)(j >> 1) & 1u);
+            if (lane == 0) ok = mbar_wait(s_full(t, b), (uint32_t)(j >> 1) & 1u);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             uint32_t sv[2][32];
-            tmem_ld32(tmem_s[b] + lane_addr, sv[0]);
-            tmem_ld32(tmem_s[b] + lane_addr + 32, sv[1]);
+            tmem_ld32(tmem_s(t, b) + lane_addr, sv[0]);
+            tmem_ld32(tmem_s(t, b) + lane_addr + 32, sv[1]);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(s_free(b));                                 // the scores are in registers
+            mbar_arrive(s_free(t, b));                              // the scores are in registers
             const int key0 = j * kBK;
-            const bool masked = key0 + kBK - 1 > pos0;              // some row of the tile does not see the whole block
+            const bool masked = key0 + kBK - 1 > tile_pos0;         // some row of the tile does not see the whole block
             // maximum of the raw scores first (the scale is positive, so it commutes with the maximum),
             // then each weight is one fused multiply-add and one ex2
             float mx = -INFINITY;
@@ -209,18 +233,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float corr = ex2(m - m_new);
             float sum = 0.f;
             // weights as bf16 into this row of the P tile: 8 pieces of 16 bytes, 128-byte swizzle
-            const uint32_t p_row = p_smem + b * kPBytes + (uint32_t)row * 128u;
+            const uint32_t p_row = p_smem + (t * 2 + b) * kPBytes + (uint32_t)row * 128u;
 #pragma unroll
             for (int c8 = 0; c8 < kBK / 8; ++c8) {
                 uint32_t packed[4];
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int c = c8 * 8 + 2 * t;
+                for (int u = 0; u < 4; ++u) {
+                    const int c = c8 * 8 + 2 * u;
                     const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
                     const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
                     sum += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                    packed[t] = *reinterpret_cast<uint32_t*>(&v);
+                    packed[u] = *reinterpret_cast<uint32_t*>(&v);
                 }
                 const uint32_t dst = p_row + (uint32_t)((c8 ^ (row & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
@@ -229,7 +253,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             l = l * corr + sum;
             if (j > 0) {
                 // the accumulator must hold block j-1 before it is rescaled (and before block j is added)
-                if (lane == 0) ok = mbar_wait(o_done, (uint32_t)(j - 1) & 1u);
+                if (lane == 0) ok = mbar_wait(o_done(t), (uint32_t)(j - 1) & 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
@@ -237,11 +261,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll 1
                     for (int c0 = 0; c0 < kD; c0 += 32) {
                         uint32_t ov[32];
-                        tmem_ld32(tmem_o + lane_addr + c0, ov);
+                        tmem_ld32(tmem_o(t) + lane_addr + c0, ov);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tmem_st32(tmem_o + lane_addr + c0, ov);
+                        tmem_st32(tmem_o(t) + lane_addr + c0, ov);
                     }
                     tmem_st_wait();
                 }
@@ -249,22 +273,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             m = m_new;
             fence_async_smem();                                     // the P tile is read by the tensor core
             tc_fence_before();
-            mbar_arrive(p_ready(b));
+            mbar_arrive(p_ready(t, b));
         }
-        if (ok && n_blocks > 0) {
-            if (lane == 0) ok = mbar_wait(o_done, (uint32_t)(n_blocks - 1) & 1u);
+        if (ok && my_blocks > 0) {
+            if (lane == 0) ok = mbar_wait(o_done(t), (uint32_t)(my_blocks - 1) & 1u);
             ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, kErrAttnSoftmax);
-        } else if (n_blocks > 0) {
+        } else if (my_blocks > 0) {
             tc_fence_after();
             const float inv = 1.f / l;
-            __nv_bfloat16* orow = out + (size_t)(tok0 + row) * o_stride + (size_t)h * kD;
+            __nv_bfloat16* orow = out + (size_t)(tok0 + t * kBQ + row) * o_stride + (size_t)h * kD;
 #pragma unroll 1
             for (int c0 = 0; c0 < kD; c0 += 32) {
                 uint32_t ov[32];
-                tmem_ld32(tmem_o + lane_addr + c0, ov);
+                tmem_ld32(tmem_o(t) + lane_addr + c0, ov);
                 tmem_ld_wait();
                 if (row < rows) {
 #pragma unroll
@@ -272,8 +296,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         uint4 u;
                         __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
-                        for (int t = 0; t < 4; ++t)
-                            hp[t] = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * t]) * inv, __uint_as_float(ov[i + 2 * t + 1]) * inv);
+                        for (int w = 0; w < 4; ++w)
+                            hp[w] = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * w]) * inv, __uint_as_float(ov[i + 2 * w + 1]) * inv);
                         *reinterpret_cast<uint4*>(orow + c0 + i) = u;
                     }
                 }
@@ -293,7 +317,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 // q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
 // lane's pages [n_pages, nkv, page_size, 128]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of
-// this step, a multiple of 128).  Head size 128 only; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
+// this step, a multiple of 256).  Head size 128 only; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
 NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
                                    long long n_pages, const int* block_table, int table_stride, const int* positions,
                                    const int* qo_indptr, const int* tiles, int n_tiles, void* out, int o_stride, int nq,

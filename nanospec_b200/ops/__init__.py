@@ -286,7 +286,8 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
                   head_dim, write_kv=True)
 
 
-TILE_Q = 128         # query rows per block of the prefill kernels
+TILE_Q = 128         # query rows per block of the m16n8k16 prefill kernel
+TILE_Q_TCGEN05 = 256 # and of the tcgen05 one (two tiles of 128)
 USE_TCGEN05_ATTENTION = True
 _TARGET_BLOCKS = 296  # decode attention wants about two blocks per SM of a B200 before it splits keys further
 
@@ -318,15 +319,15 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
 
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-                      window: int, tiles: torch.Tensor) -> None:
+                      window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head size 128 with pages of 8 to 64 tokens and no window runs
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
-    if USE_TCGEN05_ATTENTION and head_dim == 128 and window == 0 and lane.page_size in (8, 16, 32, 64) \
-            and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+    if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim == 128 and window == 0 \
+            and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         lib.call("ns_attention_prefill_tc", qkv.data_ptr(), qkv.stride(0), qkv.shape[0], lane.k.data_ptr(),
                  lane.v.data_ptr(), lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0),
-                 ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
+                 ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), tiles_tc.data_ptr(), tiles_tc.shape[0], out.data_ptr(),
                  out.stride(0), nq, nkv, head_dim, lane.page_size, float(scale), _tc(qkv.device).error.data_ptr(),
                  _stream())
         return
@@ -342,7 +343,7 @@ def _attention_plan(ctx) -> dict:
     if plan is not None:
         return plan
     if ctx.extras.get("graph"):
-        plan = {"decode_rows": None, "n_decode": ctx.n_tokens, "tiles": None, "max_kv_len": None}
+        plan = {"decode_rows": None, "n_decode": ctx.n_tokens, "tiles": None, "tiles_tc": None, "max_kv_len": None}
     else:
         starts, row = [], 0
         for n in ctx.q_lens:
@@ -350,14 +351,18 @@ def _attention_plan(ctx) -> dict:
             row += n
         decode = [s for s, n in zip(starts, ctx.q_lens) if n == 1]
         # the tiles that see the most keys come first: blocks are scheduled in this order
-        tiles = [(b, off) for b, n in enumerate(ctx.q_lens) if n > 1 for off in range(0, n, TILE_Q)]
-        tiles.sort(key=lambda t: -(ctx.kv_lens[t[0]] - ctx.q_lens[t[0]] + min(t[1] + TILE_Q, ctx.q_lens[t[0]])))
+        def make(tile_q):
+            ts = [(b, off) for b, n in enumerate(ctx.q_lens) if n > 1 for off in range(0, n, tile_q)]
+            ts.sort(key=lambda t: -(ctx.kv_lens[t[0]] - ctx.q_lens[t[0]] + min(t[1] + tile_q, ctx.q_lens[t[0]])))
+            return ts
+        tiles, tiles_tc = make(TILE_Q), make(TILE_Q_TCGEN05)
         dev = ctx.device
         plan = {
             "n_decode": len(decode),
             "decode_rows": None if len(decode) == ctx.n_tokens or not decode
             else torch.tensor(decode, dtype=torch.int32).to(dev, non_blocking=True),
             "tiles": torch.tensor(tiles, dtype=torch.int32).to(dev, non_blocking=True) if tiles else None,
+            "tiles_tc": torch.tensor(tiles_tc, dtype=torch.int32).to(dev, non_blocking=True) if tiles_tc else None,
             "max_kv_len": max((kv for kv, n in zip(ctx.kv_lens, ctx.q_lens) if n == 1), default=None),
         }
     ctx.extras["attention_plan"] = plan
@@ -382,6 +387,6 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
                          plan["max_kv_len"])
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"])
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
     return out
 
