@@ -7,7 +7,7 @@
 //   softmax          128 threads, one query row each (the row of S is read with tcgen05.ld, so the
 //                    running maximum and sum need no exchange between threads), fp32, base 2;
 //                    the weights go to shared memory as bf16, the accumulator O in TMEM is
-//                    rescaled only when some row's maximum moved
+//                    rescaled only when some row's maximum has grown by more than a factor 256
 //   O += P V         tcgen05.mma, P from shared memory, V as it lies in the cache (dim contiguous:
 //                    an MN-major operand)
 // Warp roles: warp 0 (one lane) issues the TMA loads - the keys of a block come from 64/page_size
@@ -26,7 +26,7 @@ constexpr int kBQ = 128;       // query rows per tile = UMMA M
 constexpr int kTiles = 2;      // query tiles per block: they share every key/value block
 constexpr int kBK = 64;        // keys per block
 constexpr int kD = 128;        // head size
-constexpr int kKvStages = 2;
+constexpr int kKvStages = 3;     // key/value blocks in flight: block j+2 is loaded while block j is in the softmax
 constexpr int kTcThreads = 64 + kTiles * 128;
 constexpr float kLog2eTc = 1.4426950408889634f;
 
@@ -112,6 +112,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         nblk_t[t] = rows_t[t] > 0 ? (pos0 + t * kBQ + rows_t[t] + kBK - 1) / kBK : 0;
         n_blocks = max(n_blocks, nblk_t[t]);
     }
+    const int* bt = block_table + (size_t)req * table_stride;
+    const int last_blk = (pos0 + rows_all - 1) / page_size;  // the last page that holds one of the keys seen here
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -127,8 +129,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_load_2d(q_smem + t * kQBytes, &map_q, h * kD, tok0 + t * kBQ, q_full);
             tma_load_2d(q_smem + t * kQBytes + kBQ * 128, &map_q, h * kD + 64, tok0 + t * kBQ, q_full);
         }
-        const int* bt = block_table + (size_t)req * table_stride;
-        const int last_blk = (pos0 + rows_all - 1) / page_size;  // the last page that holds one of the keys seen here
         const int pages_per_block = kBK / page_size;
         for (int j = 0; j < n_blocks; ++j) {
             const int s = j % kKvStages;
@@ -229,8 +229,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < kBK; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
             }
-            const float m_new = fmaxf(m, mx * sl);                  // block 0 holds key 0: finite from the start
-            const float corr = ex2(m - m_new);
+            // The reference point m of the exponents follows the running maximum lazily: it moves only
+            // when the maximum has grown by more than 8 (a factor 256), so the accumulator is rarely
+            // rescaled; weights up to 256 are exact enough in bf16 and the sums are fp32.  Block 0
+            // holds key 0, so m is finite from the start.
+            const float cand = mx * sl;
+            const bool jump = cand > m + 8.f;
+            const float m_new = jump ? cand : m;
+            const float corr = jump ? ex2(m - m_new) : 1.f;
             float sum = 0.f;
             // weights as bf16 into this row of the P tile: 8 pieces of 16 bytes, 128-byte swizzle
             const uint32_t p_row = p_smem + (t * 2 + b) * kPBytes + (uint32_t)row * 128u;
@@ -257,7 +263,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, m_new != m)) {          // some row's maximum moved
+                if (__any_sync(0xffffffffu, jump)) {                // some row's reference point moved
 #pragma unroll 1
                     for (int c0 = 0; c0 < kD; c0 += 32) {
                         uint32_t ov[32];
