@@ -6,14 +6,17 @@
 //   S = Q K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA), S in TMEM
 //   softmax          128 threads, one query row each (the row of S is read with tcgen05.ld, so the
 //                    running maximum and sum need no exchange between threads), fp32, base 2;
-//                    the weights go to shared memory as bf16, the accumulator O in TMEM is
-//                    rescaled only when some row's maximum has grown by more than a factor 256
-//   O += P V         tcgen05.mma, P from shared memory, V as it lies in the cache (dim contiguous:
-//                    an MN-major operand)
+//                    the weights go back to TMEM as bf16 pairs over the first half of the scores
+//                    they came from; the accumulator O in TMEM is rescaled only when some row's
+//                    maximum has grown by more than a factor 256
+//   O += P V         tcgen05.mma, P read from TMEM (so the tensor core's shared-memory reads are V
+//                    alone), V as it lies in the cache (dim contiguous: an MN-major operand)
 // Warp roles: warp 0 (one lane) issues the TMA loads - the keys of a block come from 64/page_size
 // cache pages, found through the request's block table; warp 1 (one lane) issues the MMAs and
 // owns the TMEM allocation; warps 2-5 and 6-9 are the softmax threads of the two tiles and write the output.  S is double
-// buffered in TMEM, so the scores of block j+1 are computed while block j is in the softmax.
+// buffered in TMEM, so the scores of block j+1 are computed while block j is in the softmax.  The
+// scores of block j+2 go where P of block j lies: the MMAs of one thread run in the order they were
+// issued, and that thread issues them after the product that reads P of block j.
 //
 // Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
 // block winds down.  Head sizes other than 128, page sizes other than 8/16/32/64 and windows
@@ -26,14 +29,13 @@ constexpr int kBQ = 128;       // query rows per tile = UMMA M
 constexpr int kTiles = 2;      // query tiles per block: they share every key/value block
 constexpr int kBK = 64;        // keys per block
 constexpr int kD = 128;        // head size
-constexpr int kKvStages = 3;     // key/value blocks in flight: block j+2 is loaded while block j is in the softmax
+constexpr int kKvStages = 4;     // key/value blocks in flight: later blocks are loaded while block j is in the softmax
 constexpr int kTcThreads = 64 + kTiles * 128;
 constexpr float kLog2eTc = 1.4426950408889634f;
 
 constexpr int kQBytes = kBQ * kD * 2;          // 32 KB per tile: two halves of 128 rows x 128 B
 constexpr int kKBytes = kBK * kD * 2;          // 16 KB: two halves of 64 rows x 128 B
-constexpr int kPBytes = kBQ * kBK * 2;         // 16 KB: 128 rows x 128 B
-constexpr int kSmemTc = kTiles * kQBytes + kKvStages * 2 * kKBytes + kTiles * 2 * kPBytes + 1024 + 256;
+constexpr int kSmemTc = kTiles * kQBytes + kKvStages * 2 * kKBytes + 1024 + 256;
 constexpr int kTmemColsTc = 512;               // S[tile][buffer] at (tile * 2 + buffer) * 64, O[tile] at 256 + tile * 128
 
 enum TcAttnError { kErrAttnLoader = 11, kErrAttnMma = 12, kErrAttnSoftmax = 13 };
@@ -61,18 +63,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t q_smem = base;                                   // [tile]
     const uint32_t kv_smem = q_smem + kTiles * kQBytes;             // [stage][K | V]
-    const uint32_t p_smem = kv_smem + kKvStages * 2 * kKBytes;      // [tile][buffer]
-    const uint32_t bar0 = p_smem + kTiles * 2 * kPBytes;
-    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], s_free[2], p_ready[2], o_done
+    const uint32_t bar0 = kv_smem + kKvStages * 2 * kKBytes;
+    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], p_ready[2], o_done
     const uint32_t q_full = bar0;
     auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
-    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 7 + which); };
+    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 5 + which); };
     auto s_full = [&](int t, int b) { return tile_bar(t, b); };
-    auto s_free = [&](int t, int b) { return tile_bar(t, 2 + b); };
-    auto p_ready = [&](int t, int b) { return tile_bar(t, 4 + b); };
-    auto o_done = [&](int t) { return tile_bar(t, 6); };
-    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 7);
+    auto p_ready = [&](int t, int b) { return tile_bar(t, 2 + b); };
+    auto o_done = [&](int t) { return tile_bar(t, 4); };
+    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads vary fastest: the host lists the tiles with the most keys first, and blocks are
@@ -90,7 +90,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int t = 0; t < kTiles; ++t) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(s_full(t, b), 1);
-                mbar_init(s_free(t, b), 128);
                 mbar_init(p_ready(t, b), 128);
             }
             mbar_init(o_done(t), 1);
@@ -155,11 +154,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto issue_scores = [&](int j) -> bool {
             const int s = j % kKvStages, b = j & 1;
             if (!mbar_wait(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
+            tc_fence_after();
             const uint32_t k_src = kv_smem + s * 2 * kKBytes;
             for (int t = 0; t < kTiles; ++t) {
                 if (j >= nblk_t[t]) continue;
-                if (!mbar_wait(s_free(t, b), ((uint32_t)(j >> 1) & 1u) ^ 1u)) return false;
-                tc_fence_after();
+                // S[t][b] held P of block j-2; the product that read it was issued before this
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t qa = q_smem + t * kQBytes + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
@@ -180,11 +179,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (j >= nblk_t[t]) continue;
                 if (!mbar_wait(p_ready(t, b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t p_src = p_smem + (t * 2 + b) * kPBytes;
 #pragma unroll
-                for (int kk = 0; kk < kBK / 16; ++kk)
-                    umma_bf16(tmem_o(t), smem_desc(p_src + kk * 32), smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
-                              idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kBK / 16; ++kk)  // 16 keys = 8 columns of bf16 pairs
+                    umma_bf16_ts(tmem_o(t), tmem_s(t, b) + kk * 8, smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
+                                 idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(o_done(t));    // this tile's accumulator holds blocks 0..j
             }
             umma_commit(kv_empty(s));      // the stage's keys and values have been read by every tile
@@ -212,8 +210,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_ld32(tmem_s(t, b) + lane_addr, sv[0]);
             tmem_ld32(tmem_s(t, b) + lane_addr + 32, sv[1]);
             tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(s_free(t, b));                              // the scores are in registers
             const int key0 = j * kBK;
             const bool masked = key0 + kBK - 1 > tile_pos0;         // some row of the tile does not see the whole block
             // maximum of the raw scores first (the scale is positive, so it commutes with the maximum),
@@ -238,24 +234,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float m_new = jump ? cand : m;
             const float corr = jump ? ex2(m - m_new) : 1.f;
             float sum = 0.f;
-            // weights as bf16 into this row of the P tile: 8 pieces of 16 bytes, 128-byte swizzle
-            const uint32_t p_row = p_smem + (t * 2 + b) * kPBytes + (uint32_t)row * 128u;
+            // weights as bf16 pairs over the first 32 columns of this row's scores
+            uint32_t pk[32];
 #pragma unroll
-            for (int c8 = 0; c8 < kBK / 8; ++c8) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int c = c8 * 8 + 2 * u;
-                    const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
-                    const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
-                    sum += p0 + p1;
-                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                    packed[u] = *reinterpret_cast<uint32_t*>(&v);
-                }
-                const uint32_t dst = p_row + (uint32_t)((c8 ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
-                             "r"(packed[2]), "r"(packed[3]) : "memory");
+            for (int u = 0; u < kBK / 2; ++u) {
+                const int c = 2 * u;
+                const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
+                sum += p0 + p1;
+                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                pk[u] = *reinterpret_cast<uint32_t*>(&v);
             }
+            tmem_st32(tmem_s(t, b) + lane_addr, pk);
             l = l * corr + sum;
             if (j > 0) {
                 // the accumulator must hold block j-1 before it is rescaled (and before block j is added)
@@ -273,11 +263,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
                         tmem_st32(tmem_o(t) + lane_addr + c0, ov);
                     }
-                    tmem_st_wait();
                 }
             }
             m = m_new;
-            fence_async_smem();                                     // the P tile is read by the tensor core
+            tmem_st_wait();                                         // P (and a rescaled O) are in TMEM
             tc_fence_before();
             mbar_arrive(p_ready(t, b));
         }
