@@ -121,39 +121,43 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto tmem_s = [&](int t, int b) { return tmem_base + (uint32_t)((t * 2 + b) * 64); };
     auto tmem_o = [&](int t) { return tmem_base + 256u + (uint32_t)(t * 128); };
 
-    if (warp == 0 && lane == 0) {
-        // ---------------- loader ----------------
-        mbar_expect_tx(q_full, kTiles * kQBytes);
-        for (int t = 0; t < kTiles; ++t) {  // rows past the step's tokens are zero-filled by TMA
-            tma_load_2d(q_smem + t * kQBytes, &map_q, h * kD, tok0 + t * kBQ, q_full);
-            tma_load_2d(q_smem + t * kQBytes + kBQ * 128, &map_q, h * kD + 64, tok0 + t * kBQ, q_full);
+    if (warp == 0) {
+        // ---------------- loader: the warp runs the loop, one elected lane issues ----------------
+        if (elect_one()) {
+            mbar_expect_tx(q_full, kTiles * kQBytes);
+            for (int t = 0; t < kTiles; ++t) {  // rows past the step's tokens are zero-filled by TMA
+                tma_load_2d(q_smem + t * kQBytes, &map_q, h * kD, tok0 + t * kBQ, q_full);
+                tma_load_2d(q_smem + t * kQBytes + kBQ * 128, &map_q, h * kD + 64, tok0 + t * kBQ, q_full);
+            }
         }
         const int pages_per_block = kBK / page_size;
         for (int j = 0; j < n_blocks; ++j) {
             const int s = j % kKvStages;
-            if (!mbar_wait(kv_empty(s), ((uint32_t)(j / kKvStages) & 1u) ^ 1u)) { atomicExch(error_flag, kErrAttnLoader); break; }
-            mbar_expect_tx(kv_full(s), 2 * kKBytes);
+            if (!mbar_wait_warp(kv_empty(s), ((uint32_t)(j / kKvStages) & 1u) ^ 1u)) { if (lane == 0) atomicExch(error_flag, kErrAttnLoader); break; }
+            if (elect_one()) mbar_expect_tx(kv_full(s), 2 * kKBytes);
             const uint32_t k_dst = kv_smem + s * 2 * kKBytes, v_dst = k_dst + kKBytes;
             for (int i = 0; i < pages_per_block; ++i) {
                 // pages past the last key repeat the last page: finite values that the mask hides
                 const int blk = min(j * pages_per_block + i, last_blk);
                 const int row = (bt[blk] * nkv + hk) * page_size;
                 const uint32_t off = (uint32_t)(i * page_size) * 128u;
-                tma_load_2d(k_dst + off, &map_k, 0, row, kv_full(s));
-                tma_load_2d(k_dst + kBK * 128 + off, &map_k, 64, row, kv_full(s));
-                tma_load_2d(v_dst + off, &map_v, 0, row, kv_full(s));
-                tma_load_2d(v_dst + kBK * 128 + off, &map_v, 64, row, kv_full(s));
+                if (elect_one()) {
+                    tma_load_2d(k_dst + off, &map_k, 0, row, kv_full(s));
+                    tma_load_2d(k_dst + kBK * 128 + off, &map_k, 64, row, kv_full(s));
+                    tma_load_2d(v_dst + off, &map_v, 0, row, kv_full(s));
+                    tma_load_2d(v_dst + kBK * 128 + off, &map_v, 64, row, kv_full(s));
+                }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the warp runs the loop, one elected lane issues ----------------
         constexpr uint32_t idesc_s = idesc_tc(kBK, false);
         constexpr uint32_t idesc_o = idesc_tc(kD, true);
-        bool ok = mbar_wait(q_full, 0);
+        bool ok = mbar_wait_warp(q_full, 0);
         // scores of key block j for every tile that sees it
         auto issue_scores = [&](int j) -> bool {
             const int s = j % kKvStages, b = j & 1;
-            if (!mbar_wait(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
+            if (!mbar_wait_warp(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
             tc_fence_after();
             const uint32_t k_src = kv_smem + s * 2 * kKBytes;
             for (int t = 0; t < kTiles; ++t) {
@@ -163,9 +167,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t qa = q_smem + t * kQBytes + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
                     const uint32_t kb = k_src + (kk >> 2) * (kBK * 128) + (kk & 3) * 32;
-                    umma_bf16(tmem_s(t, b), smem_desc(qa), smem_desc(kb), idesc_s, kk > 0 ? 1u : 0u);
+                    if (elect_one()) umma_bf16(tmem_s(t, b), smem_desc(qa), smem_desc(kb), idesc_s, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(s_full(t, b));
+                if (elect_one()) umma_commit(s_full(t, b));
             }
             return true;
         };
@@ -177,17 +181,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t v_src = kv_smem + s * 2 * kKBytes + kKBytes;
             for (int t = 0; t < kTiles && ok; ++t) {
                 if (j >= nblk_t[t]) continue;
-                if (!mbar_wait(p_ready(t, b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
+                if (!mbar_wait_warp(p_ready(t, b), (uint32_t)(j >> 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk)  // 16 keys = 8 columns of bf16 pairs
-                    umma_bf16_ts(tmem_o(t), tmem_s(t, b) + kk * 8, smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
-                                 idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(o_done(t));    // this tile's accumulator holds blocks 0..j
+                    if (elect_one())
+                        umma_bf16_ts(tmem_o(t), tmem_s(t, b) + kk * 8, smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
+                                     idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                if (elect_one()) umma_commit(o_done(t));    // this tile's accumulator holds blocks 0..j
             }
-            umma_commit(kv_empty(s));      // the stage's keys and values have been read by every tile
+            if (elect_one()) umma_commit(kv_empty(s));      // the stage's keys and values have been read by every tile
         }
-        if (!ok) atomicExch(error_flag, kErrAttnMma);
+        if (!ok && lane == 0) atomicExch(error_flag, kErrAttnMma);
     } else if (warp >= 2) {
         // ---------------- softmax and output: one query row per thread, one warpgroup per tile ----------------
         const int t = (warp - 2) >> 2;                             // the tile this warpgroup serves
@@ -247,22 +252,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             tmem_st32(tmem_s(t, b) + lane_addr, pk);
             l = l * corr + sum;
-            if (j > 0) {
-                // the accumulator must hold block j-1 before it is rescaled (and before block j is added)
+            if (j > 0 && __any_sync(0xffffffffu, jump)) {
+                // Some row's reference point moved: this warp's rows of the accumulator are rescaled.  They
+                // must hold block j-1 first; block j is not added before this warp has arrived below, so
+                // the barrier cannot be a phase further.
                 if (lane == 0) ok = mbar_wait(o_done(t), (uint32_t)(j - 1) & 1u);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, jump)) {                // some row's reference point moved
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kD; c0 += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem_o(t) + lane_addr + c0, ov);
-                        tmem_ld_wait();
+                for (int c0 = 0; c0 < kD; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_o(t) + lane_addr + c0, ov);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tmem_st32(tmem_o(t) + lane_addr + c0, ov);
-                    }
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_st32(tmem_o(t) + lane_addr + c0, ov);
                 }
             }
             m = m_new;
