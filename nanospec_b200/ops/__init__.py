@@ -296,11 +296,38 @@ def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
 
 
+USE_CLUSTER_DECODE = True
+
+
+def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
+    """Blocks of one cluster that share a request's keys: a power of two up to 16 that keeps the grid
+    within two blocks per SM (measured on a B200: 16 at one request, 4 at 8, 1 at 64, for contexts of
+    1,024 and 4,096), and, when the longest context is known, at least two tiles of 64 keys per block."""
+    n_splits = 1
+    while n_splits < 16 and blocks * n_splits * 2 <= _TARGET_BLOCKS:
+        n_splits *= 2
+    if max_kv_len is not None:
+        while n_splits > 1 and max_kv_len < 128 * n_splits:
+            n_splits //= 2
+    return n_splits
+
+
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None) -> None:
-    """Split-KV decode attention for the requests that bring one token (csrc/attention_decode.cu).
+    """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
+    pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
+    (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
+    memory (csrc/attention_decode.cu).
     `rows`: int32 device tensor of their token rows, or None when every row of the step is one."""
     head_tiles = -(-(nq // nkv) // 16)
+    if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0:
+        n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
+        lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+                 lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
+                 ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), _ptr(rows), n_rows, nq,
+                 nkv, head_dim, lane.page_size, float(scale), int(window), n_splits, _tc(qkv.device).error.data_ptr(),
+                 _stream())
+        return
     n_splits = max(1, min(16, -(-_TARGET_BLOCKS // (n_rows * nkv * head_tiles))))
     if max_kv_len is not None:
         # long contexts split further (measured: 4 splits are best at 4,096 keys even for 64 requests),

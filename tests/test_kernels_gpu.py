@@ -342,15 +342,47 @@ def test_decode_attention_splits_and_counters(n_req, S):
     nq, nkv, d, page = 8, 2, 128, 16
     requests = [(S - 13 * (r % 5), 1, (S - 13 * (r % 5)) // 2) for r in range(n_req)]
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=n_req * (S // page + 2), seed=S)
-    for graph in (False, True):
-        ctx.extras = {"graph": True} if graph else {}
+    for cluster in (True, False):  # the TMA kernel with its cluster, and the cp.async kernel with its counters
+        ops().USE_CLUSTER_DECODE = cluster
+        for graph in (False, True):
+            ctx.extras = {"graph": True} if graph else {}
+            for _ in range(2):
+                out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+                ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+                for r, (q, k, v, start) in enumerate(want):
+                    full = plain.plain_attention(q, k, v)
+                    torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
+    ops().USE_CLUSTER_DECODE = True
+    ops().check_kernel_errors()
+    assert int(ctx.workspace.get("attn_counters", 1, 1, torch.int32).sum()) == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(8, 2, 128, 16, 0), (4, 4, 64, 8, 0), (6, 1, 128, 32, 200), (40, 2, 64, 64, 0),
+                                                  (32, 8, 128, 64, 0), (8, 2, 128, 8, 70)])
+def test_cluster_decode_attention(nq, nkv, d, page, window):
+    """The TMA decode kernel alone, at every cluster size: contexts from one key to a few thousand, a far key
+    that must be found, a window whose first page is not the tile's first, rows picked out of a larger
+    step, twice in a row - against the plain attention."""
+    lens = [1, 5, 63, 64, 65, 130, 1000, 2100, 777]
+    requests = [(S, 1, S // 2 if S > 4 else None) for S in lens] + [(300, 40, 7)]  # the last one is not a decode row
+    ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=sum(-(-S // page) for S in lens) + 40, seed=d + page)
+    rows = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    o, lib = ops(), ops().lib
+    err = o._tc(torch.device(DEV)).error
+    for n_splits in (1, 2, 4, 8, 16):
         for _ in range(2):
             out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
-            ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
-            for r, (q, k, v, start) in enumerate(want):
-                full = plain.plain_attention(q, k, v)
+            lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+                     lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
+                     ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), rows.data_ptr(),
+                     len(lens), nq, nkv, d, page, 1.0 / math.sqrt(d), window, n_splits, err.data_ptr(),
+                     torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            o.check_kernel_errors()
+            for r, (q, k, v, start) in enumerate(want[:-1]):
+                full = plain.plain_attention(q, k, v, window=window)
                 torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
-        assert int(ctx.workspace.get("attn_counters", 1, 1, torch.int32).sum()) == 0
+            assert float(out[len(lens):].abs().sum()) == 0.0  # the prompt portion's rows are not touched
 
 
 @pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 8), (6, 1, 32), (32, 8, 64)])
