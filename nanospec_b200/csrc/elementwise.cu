@@ -247,20 +247,22 @@ NS_API int ns_residual_add(float* resid, const void* branch, int n_rows, int hid
 //   out[n, j] = silu(gu[n, j]) * gu[n, inter + j],  silu(a) = a / (1 + exp(-a)),  in float
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t n = i / inter;
     const int j = (int)(i - n * inter);
-    const float g = ns_ld(gu, n * 2 * (size_t)inter + j);
-    const float u = ns_ld(gu, n * 2 * (size_t)inter + inter + j);
+    // block == 0: [gate | up]; otherwise gate and up alternate in runs of `block` features
+    const size_t gi = block ? (size_t)(j / block) * 2 * block + j % block : (size_t)j;
+    const float g = ns_ld(gu, n * 2 * (size_t)inter + gi);
+    const float u = ns_ld(gu, n * 2 * (size_t)inter + gi + (block ? block : inter));
     ns_st(out, i, (g / (1.f + expf(-g))) * u);
 }
 
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total8) {
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total8) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -269,23 +271,29 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out,
     const size_t n = i / per_row;
     const int j = (int)(i - n * per_row) * 8;
     float g[8], u[8], y[8];
-    ld8(gu + n * 2 * (size_t)inter + j, g);
-    ld8(gu + n * 2 * (size_t)inter + inter + j, u);
+    const size_t gi = block ? (size_t)(j / block) * 2 * block + j % block : (size_t)j;  // block is a multiple of 8
+    ld8(gu + n * 2 * (size_t)inter + gi, g);
+    ld8(gu + n * 2 * (size_t)inter + gi + (block ? block : inter), u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) y[k] = (g[k] / (1.f + expf(-g[k]))) * u[k];
     st8(out + n * (size_t)inter + j, y);
 }
 
-NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype, cudaStream_t stream) {
+// out[n, j] = silu(g) * u with g, u = gate_up[n, j], gate_up[n, inter + j] (block == 0), or, when gate and up
+// alternate in runs of `block` features (a multiple of 8 that divides inter), gate_up[n, (j / block) * 2 * block +
+// j % block] and the element `block` further.
+NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int block, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)n_rows * inter;
     if (total == 0) return NS_OK;
+    if (block < 0 || (block && (block % 8 || inter % block)))
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: block=%d must be 0 or a multiple of 8 that divides %d", block, inter);
     if (inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) % 16 == 0)) {
         const size_t total8 = total / 8;
         const unsigned vblocks = (unsigned)((total8 + 255) / 256);
         if (dtype == NS_F32)
-            NS_LAUNCH((swiglu_vec_kernel<float>), vblocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total8);
+            NS_LAUNCH((swiglu_vec_kernel<float>), vblocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, block, total8);
         else if (dtype == NS_BF16)
-            NS_LAUNCH((swiglu_vec_kernel<__nv_bfloat16>), vblocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total8);
+            NS_LAUNCH((swiglu_vec_kernel<__nv_bfloat16>), vblocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total8);
         else
             NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
         NS_CHECK_LAUNCH("ns_swiglu");
@@ -293,9 +301,9 @@ NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int 
     }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == NS_F32)
-        NS_LAUNCH((swiglu_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
+        NS_LAUNCH((swiglu_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, block, total);
     else if (dtype == NS_BF16)
-        NS_LAUNCH((swiglu_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+        NS_LAUNCH((swiglu_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
     else
         NS_FAIL(NS_ERR_ARGUMENT, "ns_swiglu: unknown dtype %d", dtype);
     NS_CHECK_LAUNCH("ns_swiglu");

@@ -18,6 +18,9 @@
 // Split-K: with `splits` in {2, 4, 8} the k blocks of one output tile are divided among the blocks
 // of a thread-block cluster; each leaves its fp32 partial tile in its shared memory and, after a
 // cluster barrier, adds one slice of the features from all blocks' shared memory in rank order.
+// Gated mode (the feed-forward's packed projection): the weight rows alternate between 64 gate and
+// 64 up features, so a block's tile holds both halves of 64 outputs and the epilogue writes
+// silu(gate) * up - the activation costs no kernel and no trip through global memory.
 //
 // Every wait on an mbarrier is bounded (two seconds): when it runs out the thread records a code
 // in *error_flag and the block winds down (copies in flight are awaited, again bounded, TMEM is
@@ -58,7 +61,7 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __fl
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits,
+               OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits, int gated,
                int* __restrict__ error_flag) {
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_dyn[];
@@ -178,7 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int tok = tok0 + c * 8 + j;
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
-                            if (splits == 1) store_out(out + (size_t)tok * ldo + f, v);
+                            if (splits == 1 && !gated) store_out(out + (size_t)tok * ldo + f, v);
                             else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
@@ -194,39 +197,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
-    if (splits == 1) return;
+    if (splits == 1 && !gated) return;
 
     // The `splits` blocks of one output tile form a thread-block cluster.  Each has left its fp32
     // partial tile in its own shared memory; after a cluster barrier every block adds, in rank
     // order, one slice of the features from all the blocks' shared memory (distributed shared
     // memory) and writes that slice of the result.  Nothing goes through global memory, and the
     // sum does not depend on timing.  Blocks that gave up still take part in both barriers.
-    cluster_sync();
+    if (splits > 1) cluster_sync();
+    const uint32_t stage_addr = smem_u32(stage_f32);
+    // element idx of the partial tile of block s (a block without a cluster reads its own)
+    auto partial = [&](int idx, int s) {
+        return splits == 1 ? stage_f32[idx] : ld_cluster_f32(stage_addr + 4u * (uint32_t)idx, (uint32_t)s);
+    };
     if (!failed) {
         const int tok_n = min(BN, M_tok - tok0);
-        const int slice = BM / splits;             // features this block reduces
-        const int i0 = split * slice;
-        const uint32_t stage_addr = smem_u32(stage_f32);
-        for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
-            const int j = e / slice, i = i0 + (e - j * slice);
-            if (n0 + i >= N_feat) continue;
-            float v[kMaxSplits];
+        if (!gated) {
+            const int slice = BM / splits;             // features this block reduces
+            const int i0 = split * slice;
+            for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
+                const int j = e / slice, i = i0 + (e - j * slice);
+                if (n0 + i >= N_feat) continue;
+                float v[kMaxSplits];
 #pragma unroll
-            for (int s = 0; s < kMaxSplits; ++s)
-                v[s] = s < splits ? ld_cluster_f32(stage_addr + 4u * (uint32_t)(j * BM + i), (uint32_t)s) : 0.f;
-            float acc = 0.f;
+                for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? partial(j * BM + i, s) : 0.f;
+                float acc = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
-            store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+                for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
+                store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+            }
+        } else {
+            // features 0..63 of the tile are gates, 64..127 the matching ups: this block finishes
+            // 64 / splits outputs per token
+            const int slice = (BM / 2) / splits;
+            const int i0 = split * slice;
+            const int o0 = n0 / 2;                      // first output feature of the tile
+            for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
+                const int j = e / slice, i = i0 + (e - j * slice);
+                if (2 * (o0 + i) >= N_feat) continue;
+                float g[kMaxSplits], u[kMaxSplits];
+#pragma unroll
+                for (int s = 0; s < kMaxSplits; ++s) {
+                    g[s] = s < splits ? partial(j * BM + i, s) : 0.f;
+                    u[s] = s < splits ? partial(j * BM + BM / 2 + i, s) : 0.f;
+                }
+                float gs = 0.f, us = 0.f;
+#pragma unroll
+                for (int s = 0; s < kMaxSplits; ++s) { gs += g[s]; us += u[s]; }
+                store_out(out + (size_t)(tok0 + j) * ldo + o0 + i, (gs / (1.f + expf(-gs))) * us);
+            }
         }
     }
-    cluster_sync();  // no block may exit while another still reads its shared memory
+    if (splits > 1) cluster_sync();  // no block may exit while another still reads its shared memory
 }
 
 // ---- host side ---------------------------------------------------------------------------------
 template <int BN, typename OutT>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int M_tok, int N_feat, int k_blocks,
-              int splits, int* error_flag, cudaStream_t stream) {
+              int splits, int gated, int* error_flag, cudaStream_t stream) {
     using C = Cfg<BN>;
     static bool configured = false;
     if (!configured) {
@@ -256,7 +284,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, 
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     (void)cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, OutT>, mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks, splits,
-                             error_flag);
+                             gated, error_flag);
     NS_CHECK_LAUNCH("ns_gemm_bf16_tc");
     return NS_OK;
 }
@@ -275,11 +303,13 @@ NS_API int ns_gemm_bf16_tc_tile(int M_tok, int* tokens_per_block, int* features_
 // K, ldx and ldw must be multiples of 8 and the pointers 16-byte aligned (TMA); otherwise the call is
 // refused with NS_ERR_UNSUPPORTED.  splits is 1, 2, 4 or 8 (blocks of a cluster that share the k range).
 // `error_flag` is a device int that a timed-out wait sets.
-NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
-                           int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
+static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw, int ldo,
+                        int out_f32, int splits, int gated, int* error_flag, cudaStream_t stream) {
     if (M_tok <= 0 || N_feat <= 0) return NS_OK;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x | (uintptr_t)w) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: K=%d ldx=%d ldw=%d must be multiples of 8 and operands 16-byte aligned", K, ldx, ldw);
+    if (gated && N_feat % BM)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc_gated: %d packed features are no multiple of %d", N_feat, BM);
     const int k_blocks = (K + BK - 1) / BK;
     if (splits < 1 || splits > k_blocks || splits > kMaxSplits || (splits & (splits - 1)))
         NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: splits=%d with %d k blocks (1, 2, 4 or 8, at most the k blocks)", splits, k_blocks);
@@ -294,12 +324,26 @@ NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, i
     if (rc) return rc;
 #define NS_TC_CASE(BNN)                                                                                                 \
     case BNN:                                                                                                           \
-        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, error_flag, stream)   \
-                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, error_flag,   \
-                                                       stream);
+        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, gated, error_flag,    \
+                                               stream)                                                                  \
+                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, gated,        \
+                                                       error_flag, stream);
     switch (bn) {
         NS_TC_CASE(16) NS_TC_CASE(32) NS_TC_CASE(64) NS_TC_CASE(128) NS_TC_CASE(256)
     }
 #undef NS_TC_CASE
     NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: tile of %d tokens", bn);
+}
+
+NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
+                           int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, 0, error_flag, stream);
+}
+
+// The gated feed-forward's first half in one kernel: w[N_feat, K] holds, for every run of 64 outputs, 64 gate
+// rows followed by the 64 matching up rows (N_feat a multiple of 128);
+// out[M_tok, N_feat / 2] = silu(x * gate^T) * (x * up^T), the sums and the activation in fp32.
+NS_API int ns_gemm_bf16_tc_gated(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
+                                 int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, 1, error_flag, stream);
 }

@@ -91,13 +91,14 @@ def residual_add(resid: torch.Tensor, branch: torch.Tensor) -> torch.Tensor:
     return resid
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n, j] = silu(gate_up[n, j]) * gate_up[n, I + j]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
+    """out[n, j] = silu(gate_up[n, j]) * gate_up[n, I + j]; with `block` > 0 gate and up alternate in
+    runs of `block` features instead (gate j at (j // block) * 2 * block + j % block, up `block` further)."""
     _cuda(gate_up, out)
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype or not (gate_up.is_contiguous() and out.is_contiguous()):
         raise KernelError("swiglu: gate_up must be [N, 2I] and out [N, I], same dtype, contiguous")
-    lib.call("ns_swiglu", gate_up.data_ptr(), out.data_ptr(), n, inter, dtype_code(out.dtype), _stream())
+    lib.call("ns_swiglu", gate_up.data_ptr(), out.data_ptr(), n, inter, int(block), dtype_code(out.dtype), _stream())
     return out
 
 
@@ -223,6 +224,28 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_req: torch.T
     lib.call("ns_rope_kv_write", qkv.data_ptr(), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), inv_freq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_size, nq, nkv,
              head_dim, inv_freq.numel(), n, int(bool(write_kv)), dtype_code(qkv.dtype), _stream())
+
+
+GATE_BLOCK = 64  # gate and up rows alternate in runs of this many in a packed projection that the fused kernel takes
+
+
+def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, block: int) -> torch.Tensor:
+    """out[n, j] = silu(x @ gate_j) * (x @ up_j) for a packed projection w [2I, K]: [gate | up] when
+    `block` is 0, runs of `block` gate rows followed by the matching up rows otherwise.  A decode step
+    in bfloat16 with block == GATE_BLOCK is one tcgen05 kernel whose epilogue applies the activation;
+    everything else is the product into `scratch` [N, 2I] and the swiglu kernel."""
+    _cuda(x, w, out, scratch)
+    M, K = x.shape
+    if x.dtype == torch.bfloat16 and block == GATE_BLOCK and USE_TENSOR_CORE_GEMM and w.shape[0] % 128 == 0 \
+            and TENSOR_CORE_GEMM_MAX_TOKENS is not None and M <= TENSOR_CORE_GEMM_MAX_TOKENS \
+            and out.dtype == torch.bfloat16 and not (K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16
+                                                     or w.data_ptr() % 16 or x.stride(1) != 1 or w.stride(1) != 1):
+        if w.shape[1] != K or out.shape != (M, w.shape[0] // 2) or out.stride(1) != 1:
+            raise KernelError(f"gated_linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        lib.call("ns_gemm_bf16_tc_gated", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, w.shape[0], K, x.stride(0),
+                 w.stride(0), out.stride(0), 0, gemm_splits(M, w.shape[0], K), _tc(x.device).error.data_ptr(), _stream())
+        return out
+    return swiglu(linear(x, w, scratch), out, block)
 
 
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,

@@ -25,7 +25,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
     "ns_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "ns_residual_add": [_P, _P, _I, _I, _I, _P],
-    "ns_swiglu": [_P, _P, _I, _I, _I, _P],
+    "ns_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "ns_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "ns_rope_kv_write": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ns_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -35,6 +35,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_set_pdl": [_I],
     "ns_attention_decode_stages": [_I],
     "ns_gemm_bf16_tc": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "ns_gemm_bf16_tc_gated": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ns_attention_prefill_tc": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "ns_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
 }

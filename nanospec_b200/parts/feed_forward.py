@@ -1,5 +1,7 @@
 """The dense gated feed-forward of the reference (`MLP`, model/llama.py:187-195):
-down(silu(gate(x)) * up(x)), no biases.  Gate and up are one packed projection [gate | up].
+down(silu(gate(x)) * up(x)), no biases.  Gate and up are one packed projection: runs of 64 gate rows
+followed by the 64 matching up rows when the intermediate size is a multiple of 64 (a decode step's
+product then applies the activation in its epilogue), [gate | up] otherwise.
 
 Interface of a feed-forward part:
     forward(x, ctx) -> y        x, y: [N, hidden] in the compute dtype
@@ -25,6 +27,7 @@ class SwiGLU(Part):
         self.inter = int(spec["intermediate"])
         self.w_gate_up: torch.Tensor | None = None
         self.w_down: torch.Tensor | None = None
+        self.gate_block = 0
 
     def weight_specs(self) -> dict[str, WeightSpec]:
         return {
@@ -34,10 +37,17 @@ class SwiGLU(Part):
         }
 
     def bind(self, tensors) -> None:
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        self.gate_block = ops.GATE_BLOCK if self.inter % ops.GATE_BLOCK == 0 else 0
+        if self.gate_block:
+            b = self.gate_block
+            packed = torch.stack([gate.view(self.inter // b, b, self.hidden), up.view(self.inter // b, b, self.hidden)], dim=1)
+            self.w_gate_up = packed.reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = ops.linear(x, self.w_gate_up, ctx.buffer("gate_up", 2 * self.inter))
-        act = ops.swiglu(gu, ctx.buffer("ffn_act", self.inter))
+        act = ops.gated_linear(x, self.w_gate_up, ctx.buffer("ffn_act", self.inter), ctx.buffer("gate_up", 2 * self.inter),
+                               self.gate_block)
         return ops.linear(act, self.w_down, ctx.buffer("branch", self.hidden))

@@ -69,6 +69,39 @@ def test_split_k_over_a_cluster_is_deterministic(M, N, K, splits):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("M,inter,K,splits", [(1, 64, 64, 1), (8, 14336, 4096, 1), (16, 384, 1024, 2), (5, 128, 8192, 8), (40, 192, 520, 4),
+                                              (300, 256, 256, 1)])
+def test_gated_epilogue(M, inter, K, splits):
+    """The packed projection with gate and up rows alternating in runs of 64: the kernel's epilogue applies
+    silu(gate) * up; against float64, and against the unfused product followed by the swiglu kernel."""
+    g = torch.Generator().manual_seed(inter + M)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(inter, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(inter, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    w = torch.stack([gate.view(inter // 64, 64, K), up.view(inter // 64, 64, K)], dim=1).reshape(2 * inter, K).contiguous()
+    gd, ud = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    o = ops()
+    out = torch.full((M, inter), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.lib.call("ns_gemm_bf16_tc_gated", x.data_ptr(), w.data_ptr(), out.data_ptr(), M, 2 * inter, K, x.stride(0), w.stride(0),
+               out.stride(0), 0, splits, o._tc(torch.device(DEV)).error.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    o.check_kernel_errors()
+    err = (out.double() - want).abs().max().item()
+    assert err <= 2.0 ** -8 * want.abs().max().item() + 1e-3, err
+    # the two-kernel path on the same packed weights (it rounds the products to bf16 first)
+    scratch = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    out2 = torch.empty_like(out)
+    o.swiglu(o.linear(x, w, scratch), out2, 64)
+    torch.testing.assert_close(out2.float(), want.float(), rtol=3e-2, atol=3e-2)
+    # and what the part calls
+    out3 = torch.empty_like(out)
+    o.gated_linear(x, w, out3, scratch, 64)
+    if M <= 16:
+        assert torch.equal(out3, out) or splits != o.gemm_splits(M, 2 * inter, K)
+    torch.testing.assert_close(out3.float(), want.float(), rtol=3e-2, atol=3e-2)
+
+
 def test_strided_rows_and_output():
     x, w, want = case(24, 192, 128, 5, ldx=136, ldw=256)
     wide = torch.zeros(24, 400, dtype=torch.bfloat16, device=DEV)

@@ -81,6 +81,14 @@ def test_swiglu_and_residual_add(dtype):
     f = gu.float()
     want = torch.nn.functional.silu(f[:, :inter]) * f[:, inter:]
     torch.testing.assert_close(out.float(), want, **tol(dtype))
+    # gate and up alternating in runs of 32 features
+    inter2, block = 320, 32
+    gu2 = (torch.randn(n, 2 * inter2, generator=g) * 4).to(dtype).to(DEV)
+    out2 = torch.empty(n, inter2, dtype=dtype, device=DEV)
+    ops().swiglu(gu2, out2, block)
+    f2 = gu2.float().view(n, inter2 // block, 2, block)
+    want2 = (torch.nn.functional.silu(f2[:, :, 0]) * f2[:, :, 1]).reshape(n, inter2)
+    torch.testing.assert_close(out2.float(), want2, **tol(dtype))
     resid = torch.randn(n, inter, generator=g).to(DEV)
     want_r = resid + out.float()
     ops().residual_add(resid, out)
