@@ -8,7 +8,9 @@
 // the bytes), and four warps consume them: each takes 16 keys of every tile, computes scores and the
 // weighted sum on the tensor cores (m16n8k16, the group's query heads padded to 16 rows, the query
 // fragments read straight from global memory), and keeps the softmax in fp32 (online, base 2).
-// No block-wide barrier inside the loop: a warp waits for the tile's mbarrier and gives the stage
+// The loads of all keys but the token's own are issued before the kernel waits for its predecessor in
+// the stream (programmatic dependent launch), so the cache streams in while the query is still
+// being rotated.  No block-wide barrier inside the loop: a warp waits for the tile's mbarrier and gives the stage
 // back through another.  At the end the four warps' partial results are combined in shared memory,
 // and the blocks of the cluster combine theirs through distributed shared memory, each block
 // writing one slice of the output in split order - no scratch in global memory, no atomics, and a
@@ -77,7 +79,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         fence_async_smem();
     }
     __syncthreads();
-    ns_pdl_wait();  // everything below reads what earlier kernels wrote (q, the cache, the step's description)
+    // The step's description and every key but the newest were written before the previous kernel
+    // started (by a copy, or by earlier steps): they are read before this kernel waits for it.  Only the
+    // query and the page slot of the token's own key come from the predecessor.
 
     const int n_splits = gridDim.x, split = blockIdx.x, z = blockIdx.z;
     const int n = rows ? rows[z] : z;  // the token this cluster works for
@@ -111,8 +115,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int pages_per_tile = kKeys >> page_shift;
         const int first_page = kstart >> page_shift;          // pages before it may have been given back
         const int last_page = (kend - 1) >> page_shift;       // pages past it repeat it: finite values that the mask hides
+        bool waited = false;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % kDtStages;
+            // the tile with the token's own key, and whatever needs a stage back from the other warps (they
+            // wait for the query first), come after the wait for the previous kernel
+            if (!waited && (t >= kDtStages || k0 + (t + 1) * kKeys > pos)) {
+                ns_pdl_wait();
+                waited = true;
+            }
             if (t >= kDtStages && !mbar_wait_warp(empty(s), (uint32_t)(t / kDtStages - 1) & 1u)) {
                 if (lane == 0) atomicExch(error_flag, kErrDecodeLoader);
                 break;
@@ -138,6 +149,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
     } else {
         // ---------------- four warps: 16 keys of every tile each ----------------
+        ns_pdl_wait();  // the query comes from the previous kernel, and nothing is written before it is done
         uint32_t qf[D / 16][4];
         {
             const int g = lane >> 2, c2 = 2 * (lane & 3);

@@ -134,8 +134,15 @@ __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
-    ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float scratch[32];
+    // the gain is a weight: it is fetched while the previous kernel is still running
+    float g[CHUNKS][8];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int h = (threadIdx.x + c * THREADS) * 8;
+        if (h < hidden) ld8(gain + h, g[c]);
+    }
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     const int j = blockIdx.x;
     const int row = rows ? rows[j] : j;
     float* r = resid + (size_t)row * hidden;
@@ -164,10 +171,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, 
     for (int c = 0; c < CHUNKS; ++c) {
         const int h = (threadIdx.x + c * THREADS) * 8;
         if (h < hidden) {
-            float g[8], y[8];
-            ld8(gain + h, g);
+            float y[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = v[c][i] * inv * g[i];
+            for (int i = 0; i < 8; ++i) y[i] = v[c][i] * inv * g[c][i];
             st8(o + h, y);
         }
     }

@@ -20,7 +20,8 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
                      T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d,
                      int rot_pairs, int write_kv) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
-    ns_pdl_wait();               // everything below sees the previous kernel's results
+    // The step's description, the block table and the angles do not come from the previous kernel: they
+    // are read and computed before this kernel waits for it; only the projection itself comes after.
     const int n = blockIdx.x, hh = blockIdx.y;
     const int req = token_req[n];
     if (req < 0) return;
@@ -36,12 +37,16 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
         // cache[page, kv head, offset, :]
         dst = (is_v ? v_cache : k_cache) + (((size_t)page * nkv + hk) * page_size + pos % page_size) * d;
     }
+    const int j0 = threadIdx.x;  // a block of 128 threads covers head sizes up to 256 in one pass
+    float s0 = 0.f, c0 = 1.f;
+    if (!is_v && j0 < rot_pairs && j0 < half) sincosf((float)pos * inv_freq[j0], &s0, &c0);
+    ns_pdl_wait();               // everything below sees the previous kernel's results
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         const float x1 = ns_ld(x, j), x2 = ns_ld(x, j + half);
         float o1 = x1, o2 = x2;
         if (!is_v && j < rot_pairs) {
-            float s, c;
-            sincosf((float)pos * inv_freq[j], &s, &c);
+            float s = s0, c = c0;
+            if (j != j0) sincosf((float)pos * inv_freq[j], &s, &c);
             // spelled out so that both kernels of this file round alike
             o1 = __fmaf_rn(x1, c, -__fmul_rn(x2, s));
             o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
