@@ -21,6 +21,14 @@
 // Gated mode (the feed-forward's packed projection): the weight rows alternate between 64 gate and
 // 64 up features, so a block's tile holds both halves of 64 outputs and the epilogue writes
 // silu(gate) * up - the activation costs no kernel and no trip through global memory.
+// Two more epilogues let a decode step do without its norm kernels (16 tokens at most):
+//   sink:  the output is a branch of the residual stream that an RMSNorm follows.  The block adds
+//          its features to the fp32 residual, writes gain * residual in bf16 for the next product and
+//          the sum of squares of its features per token; the norm's scale, one number per token, is
+//          still missing from those activations.
+//   scale: the activations came from such a sink.  The epilogue adds up the partial sums of squares of
+//          each token (in a fixed order), and multiplies the token's outputs by
+//          rsqrt(sum / hidden + eps) - a product is linear in a per-token scale of its input.
 //
 // Every wait on an mbarrier is bounded (two seconds): when it runs out the thread records a code
 // in *error_flag and the block winds down (copies in flight are awaited, again bounded, TMEM is
@@ -34,6 +42,21 @@ constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzl
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kMaxSplits = 8;
+
+// What the epilogue does besides storing the product (all pointers null: nothing).
+struct GemmEpilogue {
+    int gated;                    // silu(gate) * up on alternating runs of 64 features
+    // scale: out rows *= rsqrt(sum_p row_partials[token, p] / hidden + eps)
+    const float* row_partials;    // [tokens, n_partials]
+    int n_partials;
+    float inv_hidden, eps;
+    // sink: resid += product; sink_x = bf16(gain * resid); sink_partials[token, block] = sum of resid^2 over the block's features
+    float* sink_resid;            // [tokens, sink_ld]
+    const float* sink_gain;       // [features]
+    __nv_bfloat16* sink_x;        // [tokens, sink_ld]
+    float* sink_partials;         // [tokens, feature tiles * splits]
+    int sink_ld;
+};
 
 enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrainWait = 4 };
 
@@ -61,8 +84,13 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __fl
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits, int gated,
+               OutT* __restrict__ out, int ldo, int M_tok, int N_feat, int k_blocks, int splits, const GemmEpilogue ep,
                int* __restrict__ error_flag) {
+    const int gated = ep.gated;
+    const bool sink = ep.sink_resid != nullptr;
+    // per-token scale (scale mode) and squares of the finished residual (sink mode); both modes are
+    // offered for tiles of 16 tokens only
+    __shared__ float inv_s[16];
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -75,6 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ int failed;
     // after the last MMA the pipeline stages are free: the split-K partial tile is staged there
     float* stage_f32 = reinterpret_cast<float*>(smem_dyn + (base - smem_u32(smem_dyn)));
+    float* sq_s = stage_f32 + BN * BM;  // sink mode (16 tokens): [16][BM + 1] squares, behind the partial tile
 
     ns_pdl_launch_dependents();  // the next kernel may be scheduled; it waits for this one before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,6 +190,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ns_pdl_wait();           // before anything is written that the previous kernel may still read
         const int q = warp & 3;  // the TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;
+        if (BN == 16) {
+            // while the products run: each token's scale, one warp per token, partial sums in ascending order
+            for (int t = warp - 2; t < 16; t += 4) {
+                float inv = 1.f;
+                if (ep.row_partials && tok0 + t < M_tok) {
+                    const float* p = ep.row_partials + (size_t)(tok0 + t) * ep.n_partials;
+                    float acc = 0.f;
+                    for (int i = lane; i < ep.n_partials; i += 32) acc += p[i];
+                    inv = rsqrtf(ns_warp_sum(acc) * ep.inv_hidden + ep.eps);
+                }
+                if (lane == 0) inv_s[t] = inv;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        }
         bool ok = true;
         if (lane == 0) ok = mbar_wait(accum_bar, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -181,7 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int tok = tok0 + c * 8 + j;
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
-                            if (splits == 1 && !gated) store_out(out + (size_t)tok * ldo + f, v);
+                            if (splits == 1 && !gated && !sink) store_out(out + (size_t)tok * ldo + f, BN == 16 ? v * inv_s[c * 8 + j] : v);
                             else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
@@ -197,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
-    if (splits == 1 && !gated) return;
+    if (splits == 1 && !gated && !sink) return;
 
     // The `splits` blocks of one output tile form a thread-block cluster.  Each has left its fp32
     // partial tile in its own shared memory; after a cluster barrier every block adds, in rank
@@ -224,7 +267,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float acc = 0.f;
 #pragma unroll
                 for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
-                store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+                if (BN == 16) acc *= inv_s[j];
+                if (BN == 16 && sink) {
+                    const size_t o = (size_t)(tok0 + j) * ep.sink_ld + n0 + i;
+                    const float r = ep.sink_resid[o] + acc;
+                    ep.sink_resid[o] = r;
+                    ep.sink_x[o] = __float2bfloat16_rn(r * ep.sink_gain[n0 + i]);
+                    sq_s[j * (BM + 1) + (i - i0)] = r * r;
+                } else {
+                    store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+                }
+            }
+            if (BN == 16 && sink) {
+                // the block's share of each token's sum of squares, added in feature order
+                __syncthreads();
+                if ((int)threadIdx.x < tok_n) {
+                    float t = 0.f;
+                    for (int k = 0; k < slice; ++k) t += sq_s[threadIdx.x * (BM + 1) + k];
+                    ep.sink_partials[(size_t)(tok0 + threadIdx.x) * (gridDim.x * splits) + blockIdx.x * splits + split] = t;
+                }
             }
         } else {
             // features 0..63 of the tile are gates, 64..127 the matching ups: this block finishes
@@ -244,6 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float gs = 0.f, us = 0.f;
 #pragma unroll
                 for (int s = 0; s < kMaxSplits; ++s) { gs += g[s]; us += u[s]; }
+                if (BN == 16) { gs *= inv_s[j]; us *= inv_s[j]; }
                 store_out(out + (size_t)(tok0 + j) * ldo + o0 + i, (gs / (1.f + expf(-gs))) * us);
             }
         }
@@ -254,7 +316,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // ---- host side ---------------------------------------------------------------------------------
 template <int BN, typename OutT>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int M_tok, int N_feat, int k_blocks,
-              int splits, int gated, int* error_flag, cudaStream_t stream) {
+              int splits, const GemmEpilogue& ep, int* error_flag, cudaStream_t stream) {
     using C = Cfg<BN>;
     static bool configured = false;
     if (!configured) {
@@ -284,7 +346,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, 
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     (void)cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, OutT>, mw, mx, (OutT*)out, ldo, M_tok, N_feat, k_blocks, splits,
-                             gated, error_flag);
+                             ep, error_flag);
     NS_CHECK_LAUNCH("ns_gemm_bf16_tc");
     return NS_OK;
 }
@@ -304,7 +366,8 @@ NS_API int ns_gemm_bf16_tc_tile(int M_tok, int* tokens_per_block, int* features_
 // refused with NS_ERR_UNSUPPORTED.  splits is 1, 2, 4 or 8 (blocks of a cluster that share the k range).
 // `error_flag` is a device int that a timed-out wait sets.
 static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw, int ldo,
-                        int out_f32, int splits, int gated, int* error_flag, cudaStream_t stream) {
+                        int out_f32, int splits, const GemmEpilogue& ep, int* error_flag, cudaStream_t stream) {
+    const int gated = ep.gated;
     if (M_tok <= 0 || N_feat <= 0) return NS_OK;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x | (uintptr_t)w) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: K=%d ldx=%d ldw=%d must be multiples of 8 and operands 16-byte aligned", K, ldx, ldw);
@@ -316,6 +379,11 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: no error flag");
     int bn, bm;
     ns_gemm_bf16_tc_tile(M_tok, &bn, &bm);
+    if ((ep.row_partials || ep.sink_resid) && bn != 16)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: the norm epilogues take 16 tokens at most, not %d", M_tok);
+    if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || !ep.sink_partials))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink needs %d features to be a multiple of %d, and all its tensors", N_feat, BM);
+    if (ep.row_partials && ep.n_partials < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: n_partials=%d", ep.n_partials);
     if ((M_tok + bn - 1) / bn > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: too many token tiles");
     CUtensorMap mw, mx;
     int rc = ns_make_map_bf16(&mw, w, N_feat, K, ldw, BM, "ns_gemm_bf16_tc");
@@ -324,9 +392,9 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
     if (rc) return rc;
 #define NS_TC_CASE(BNN)                                                                                                 \
     case BNN:                                                                                                           \
-        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, gated, error_flag,    \
+        return out_f32 ? launch_tc<BNN, float>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, ep, error_flag,       \
                                                stream)                                                                  \
-                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, gated,        \
+                       : launch_tc<BNN, __nv_bfloat16>(mw, mx, out, ldo, M_tok, N_feat, k_blocks, splits, ep,           \
                                                        error_flag, stream);
     switch (bn) {
         NS_TC_CASE(16) NS_TC_CASE(32) NS_TC_CASE(64) NS_TC_CASE(128) NS_TC_CASE(256)
@@ -337,7 +405,8 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
 
 NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
                            int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, 0, error_flag, stream);
+    GemmEpilogue ep = {};
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
 }
 
 // The gated feed-forward's first half in one kernel: w[N_feat, K] holds, for every run of 64 outputs, 64 gate
@@ -345,5 +414,31 @@ NS_API int ns_gemm_bf16_tc(const void* x, const void* w, void* out, int M_tok, i
 // out[M_tok, N_feat / 2] = silu(x * gate^T) * (x * up^T), the sums and the activation in fp32.
 NS_API int ns_gemm_bf16_tc_gated(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
                                  int ldo, int out_f32, int splits, int* error_flag, cudaStream_t stream) {
-    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, 1, error_flag, stream);
+    GemmEpilogue ep = {};
+    ep.gated = 1;
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
+}
+
+// The same products with the norm epilogues (16 tokens at most).
+//   row_partials [M_tok, n_partials] (or null): every output row is multiplied by
+//       rsqrt(sum of the row's partials / hidden + eps) - the activations x were left unscaled by a sink;
+//   sink_resid [M_tok, sink_ld] (or null; not with gated): the product is added to it, sink_x [M_tok, sink_ld] gets
+//       bf16(sink_gain * resid) and sink_partials [M_tok, n_sink_partials] the sums of squares per block, where
+//       n_sink_partials = (N_feat / 128) * splits; `out` is not written.
+NS_API int ns_gemm_bf16_tc_norm(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
+                                int ldo, int out_f32, int splits, int gated, const float* row_partials, int n_partials,
+                                int hidden, float eps, float* sink_resid, const float* sink_gain, void* sink_x,
+                                float* sink_partials, int sink_ld, int* error_flag, cudaStream_t stream) {
+    GemmEpilogue ep = {};
+    ep.gated = gated;
+    ep.row_partials = row_partials;
+    ep.n_partials = n_partials;
+    ep.inv_hidden = hidden > 0 ? 1.f / (float)hidden : 0.f;
+    ep.eps = eps;
+    ep.sink_resid = sink_resid;
+    ep.sink_gain = sink_gain;
+    ep.sink_x = (__nv_bfloat16*)sink_x;
+    ep.sink_partials = sink_partials;
+    ep.sink_ld = sink_ld;
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
 }

@@ -6,6 +6,7 @@ except `linear` in bfloat16, which may hand a plain matrix product to cuBLAS.
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 
 import torch
 
@@ -171,14 +172,104 @@ def linear_tensor_core(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, spli
     return True
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+FUSE_NORM = True  # a decode step's products take over the residual sum and the norm that follows them
+
+
+@dataclass
+class NormSink:
+    """Where a product's output goes when the residual sum and the RMSNorm that follow are folded
+    into its epilogue: `resid` [N, H] float32 is updated in place, `gain` [H] and `eps` are the norm's."""
+
+    resid: torch.Tensor
+    gain: torch.Tensor
+    eps: float
+    workspace: object  # parts.context.Workspace: the buffers of the result come from it
+
+
+@dataclass
+class RowScaled:
+    """Normed activations that still lack the norm's scale: `x` [N, H] = gain * resid in the compute
+    dtype and `partials` [N, P] float32, per-row partial sums of resid^2.  Row n's scale is
+    rsqrt(sum(partials[n]) / hidden + eps); the product that reads `x` applies it to its output rows
+    (a product is linear in a per-row scale of its input).  `gain` identifies the norm it stands for."""
+
+    x: torch.Tensor
+    partials: torch.Tensor
+    hidden: int
+    eps: float
+    gain: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+
+def _tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    K = x.shape[1]
+    return not (K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.stride(1) != 1 or w.stride(1) != 1
+                or x.data_ptr() % 16 or w.data_ptr() % 16)
+
+
+def norm_fusion_ok(n_tokens: int, dtype: torch.dtype, *weights: torch.Tensor) -> bool:
+    """Whether a step of `n_tokens` in `dtype` may hand normed activations on as `RowScaled` to products
+    with these weights (and fold a norm into a product with them): the tcgen05 kernel with a tile of 16
+    tokens, feature counts in multiples of 128, rows that TMA can address."""
+    if not (FUSE_NORM and USE_TENSOR_CORE_GEMM and dtype == torch.bfloat16 and 0 < n_tokens <= 16):
+        return False
+    if TENSOR_CORE_GEMM_MAX_TOKENS is not None and n_tokens > TENSOR_CORE_GEMM_MAX_TOKENS:
+        return False
+    return all(w.dtype == torch.bfloat16 and w.shape[0] % 128 == 0 and w.shape[1] % 8 == 0 and w.stride(1) == 1
+               and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 for w in weights)
+
+
+def _linear_norm(x, w: torch.Tensor, out: torch.Tensor | None, gated: bool, sink: NormSink | None):
+    """The tcgen05 product with the norm epilogues: x a tensor or RowScaled; returns `out`, or the
+    RowScaled that the sink produced."""
+    scaled = x if isinstance(x, RowScaled) else None
+    xt = scaled.x if scaled is not None else x
+    M, K = xt.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not _tma_ok(xt, w) or M > 16:
+        raise KernelError(f"linear: the norm epilogues cannot take x {tuple(xt.shape)}, w {tuple(w.shape)}")
+    splits = gemm_splits(M, N, K)
+    res = None
+    if sink is not None:
+        if gated or N % 128 or sink.resid.shape != (M, N) or not sink.resid.is_contiguous():
+            raise KernelError("linear: a norm sink takes an ungated product whose width is the residual's, a multiple of 128")
+        ws = sink.workspace
+        res = RowScaled(ws.get("sink_x", M, N, torch.bfloat16), ws.get("sink_partials", M, (N // 128) * splits, torch.float32),
+                        N, sink.eps, sink.gain)
+    elif out is None or out.shape != (M, N // 2 if gated else N) or out.stride(1) != 1:
+        raise KernelError("linear: the output does not fit the product")
+    lib.call("ns_gemm_bf16_tc_norm", xt.data_ptr(), w.data_ptr(), _ptr(out), M, N, K, xt.stride(0), w.stride(0),
+             out.stride(0) if out is not None else 0, int(out is not None and out.dtype == torch.float32), splits, int(gated),
+             _ptr(scaled.partials if scaled is not None else None), scaled.partials.shape[1] if scaled is not None else 0,
+             scaled.hidden if scaled is not None else 0, float(scaled.eps) if scaled is not None else 0.0,
+             _ptr(sink.resid if sink is not None else None), _ptr(sink.gain if sink is not None else None),
+             _ptr(res.x if res is not None else None), _ptr(res.partials if res is not None else None),
+             N if sink is not None else 0, _tc(xt.device).error.data_ptr(), _stream())
+    return res if res is not None else out
+
+
+def linear(x, w: torch.Tensor, out: torch.Tensor, sink: NormSink | None = None):
     """out[M, N] = x[M, K] @ w[N, K]^T with fp32 accumulation.
+
+    `x` may be a `RowScaled` (its rows' scale is applied to the output).  With a `sink` that the product
+    can fold in (`norm_fusion_ok`), nothing is written to `out`: the residual is updated and a `RowScaled`
+    for the norm that follows is returned; otherwise `out` is returned and the caller runs the norm.
 
     float32: the CUDA-core kernel (true fp32, k-ascending sums, independent of M).
     bfloat16: the tcgen05 kernel; operands that TMA cannot address (K or a row stride that is no
     multiple of 8) are a plain matrix product for cuBLAS, as the reference hands its `nn.Linear`
     calls to it (model/llama.py:175,184,195).  `out` may be bfloat16 or float32.
     """
+    if isinstance(x, RowScaled) or (sink is not None and norm_fusion_ok(x.shape[0], x.dtype, w)
+                                    and sink.resid.shape[1] == w.shape[0] and _tma_ok(x, w)):
+        return _linear_norm(x, w, out, False, sink)
     _cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
@@ -233,7 +324,11 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: t
     """out[n, j] = silu(x @ gate_j) * (x @ up_j) for a packed projection w [2I, K]: [gate | up] when
     `block` is 0, runs of `block` gate rows followed by the matching up rows otherwise.  A decode step
     in bfloat16 with block == GATE_BLOCK is one tcgen05 kernel whose epilogue applies the activation;
-    everything else is the product into `scratch` [N, 2I] and the swiglu kernel."""
+    everything else is the product into `scratch` [N, 2I] and the swiglu kernel.  `x` may be a `RowScaled`."""
+    if isinstance(x, RowScaled):
+        if block == GATE_BLOCK and out.dtype == torch.bfloat16:
+            return _linear_norm(x, w, out, True, None)
+        return swiglu(_linear_norm(x, w, scratch, False, None), out, block)
     _cuda(x, w, out, scratch)
     M, K = x.shape
     if x.dtype == torch.bfloat16 and block == GATE_BLOCK and USE_TENSOR_CORE_GEMM and w.shape[0] % 128 == 0 \

@@ -8,6 +8,8 @@ Interface of a mixer part:
     cache_need() -> CacheNeed | None      paged storage wanted per token
     state_need() -> StateNeed | None      fixed-size state wanted per request
     forward(x, ctx, lane, writes) -> y    x, y: [N, hidden] in the compute dtype
+A mixer may also take part in folding the norms into its products (`Part.takes_row_scaled`,
+`Part.feeds_norm_sink`); this one does.
 """
 
 from __future__ import annotations
@@ -63,7 +65,13 @@ class GQAAttention(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, lane: LaneView, writes: bool = True) -> torch.Tensor:
+    def takes_row_scaled(self, n_tokens: int) -> bool:
+        return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_qkv)
+
+    def feeds_norm_sink(self, n_tokens: int) -> bool:
+        return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_o)
+
+    def forward(self, x, ctx: StepContext, lane: LaneView, writes: bool = True, sink: ops.NormSink | None = None):
         qkv = ops.linear(x, self.w_qkv, ctx.buffer("qkv", self.q_size + 2 * self.kv_size))
         if self.position is not None:
             self.position.rotate_and_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes)
@@ -71,4 +79,4 @@ class GQAAttention(Part):
             ops.kv_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn_out", self.q_size)
         ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window)
-        return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden))
+        return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)

@@ -44,6 +44,17 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         """Receives the tensors named by `weight_specs`, already on the device and cast."""
 
+    # ---- optional: folding the norms into products (a decode step's mixers and feed-forwards) ----
+    def takes_row_scaled(self, n_tokens: int) -> bool:
+        """True when `forward` may be given its input as an `ops.RowScaled` (normed activations whose
+        per-row scale the part's first product applies) in a step of `n_tokens` tokens."""
+        return False
+
+    def feeds_norm_sink(self, n_tokens: int) -> bool:
+        """True when `forward` takes `sink=ops.NormSink(...)` in such a step: its last product then adds
+        its output to the residual stream itself and returns an `ops.RowScaled` for the norm that follows."""
+        return False
+
 
 @dataclass(frozen=True)
 class CacheNeed:

@@ -5,6 +5,7 @@ product then applies the activation in its epilogue), [gate | up] otherwise.
 
 Interface of a feed-forward part:
     forward(x, ctx) -> y        x, y: [N, hidden] in the compute dtype
+and, optionally, the folding of norms into its products (`Part.takes_row_scaled`, `Part.feeds_norm_sink`).
 """
 
 from __future__ import annotations
@@ -47,7 +48,13 @@ class SwiGLU(Part):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def takes_row_scaled(self, n_tokens: int) -> bool:
+        return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_gate_up)
+
+    def feeds_norm_sink(self, n_tokens: int) -> bool:
+        return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_down)
+
+    def forward(self, x, ctx: StepContext, sink: ops.NormSink | None = None):
         act = ops.gated_linear(x, self.w_gate_up, ctx.buffer("ffn_act", self.inter), ctx.buffer("gate_up", 2 * self.inter),
                                self.gate_block)
-        return ops.linear(act, self.w_down, ctx.buffer("branch", self.hidden))
+        return ops.linear(act, self.w_down, ctx.buffer("branch", self.hidden), sink=sink)

@@ -68,8 +68,15 @@ class DecoderModel:
         when `all_rows`, or None when nothing is wanted."""
         resid = self.embedding.forward(ctx)
         pending = None
-        for run in self.recipe.order:
-            resid, pending = self.blocks[run.layer].forward(resid, pending, ctx, ctx.lanes[run.lane], run.writes)
+        order = self.recipe.order
+        for i, run in enumerate(order):
+            # the block that runs next: its first norm may be folded into this block's last product
+            follow = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            block = self.blocks[run.layer]
+            if follow is not None and getattr(block, "takes_follow", False):
+                resid, pending = block.forward(resid, pending, ctx, ctx.lanes[run.lane], run.writes, follow=follow)
+            else:
+                resid, pending = block.forward(resid, pending, ctx, ctx.lanes[run.lane], run.writes)
         if want_rows is None and not all_rows:
             return None
         return self.final_norm.add_norm(resid, pending, ctx, rows=want_rows, out_name="final_normed")

@@ -9,6 +9,9 @@ Interface of a norm part:
         resid   [N, H] float32, updated in place with `pending` when that is given
         pending [N, H] compute dtype or None: a branch output not yet added to the stream
         rows    int32 device tensor or None: only these rows are produced (resid untouched)
+    sink(resid, ctx) -> ops.NormSink    what a product needs to fold this norm and the sum before it
+                                        into its epilogue; `add_norm` hands the product's
+                                        `ops.RowScaled` result on unchanged
 """
 
 from __future__ import annotations
@@ -35,8 +38,16 @@ class RMSNorm(Part):
     def bind(self, tensors) -> None:
         self.gain = tensors["weight"].contiguous()
 
-    def add_norm(self, resid: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext,
-                 rows: torch.Tensor | None = None, out_name: str = "normed") -> torch.Tensor:
+    def sink(self, resid: torch.Tensor, ctx: StepContext) -> ops.NormSink:
+        return ops.NormSink(resid, self.gain, self.eps, ctx.workspace)
+
+    def add_norm(self, resid: torch.Tensor, pending, ctx: StepContext,
+                 rows: torch.Tensor | None = None, out_name: str = "normed"):
+        if isinstance(pending, ops.RowScaled):
+            # a product has added its output to the stream and prepared this norm's input already
+            if pending.gain is not self.gain or rows is not None:
+                raise ValueError("a RowScaled reached a norm it was not made for")
+            return pending
         n = resid.shape[0] if rows is None else rows.numel()
         out = ctx.buffer(out_name, self.hidden, rows=n)
         return ops.add_rmsnorm(resid, pending, self.gain, self.eps, out, rows=rows)

@@ -102,6 +102,49 @@ def test_gated_epilogue(M, inter, K, splits):
     torch.testing.assert_close(out3.float(), want.float(), rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("M,H,K,N2", [(1, 128, 64, 256), (8, 4096, 4096, 6144), (16, 256, 520, 384), (5, 384, 14336, 128)])
+def test_norm_epilogues(M, H, K, N2):
+    """A product that feeds a norm sink (residual sum, gain, partial sums of squares) and the products
+    that apply the missing per-row scale, plain and gated - against float64, twice for determinism."""
+    from types import SimpleNamespace
+    from nanospec_b200.parts import Workspace
+    o = ops()
+    g = torch.Generator().manual_seed(M + H)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    resid0 = torch.randn(M, H, generator=g).to(DEV)
+    gain = (1 + 0.1 * torch.randn(H, generator=g)).to(DEV)
+    w2 = (torch.randn(N2, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+    eps = 1e-5
+    ws = Workspace(torch.device(DEV))
+    assert o.norm_fusion_ok(M, torch.bfloat16, w, w2)
+    r_want = resid0.double() + x.double() @ w.double().T
+    scale = torch.rsqrt((r_want ** 2).mean(dim=1, keepdim=True) + eps)
+    results = []
+    for _ in range(2):
+        resid = resid0.clone()
+        rs = o.linear(x, w, torch.empty(M, H, dtype=torch.bfloat16, device=DEV), sink=o.NormSink(resid, gain, eps, ws))
+        assert isinstance(rs, o.RowScaled) and rs.gain is gain
+        torch.testing.assert_close(resid.double(), r_want, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(rs.x.double(), (gain.double() * r_want), rtol=2 ** -7, atol=1e-3)
+        got_scale = torch.rsqrt(rs.partials.double().sum(dim=1, keepdim=True) / H + eps)
+        torch.testing.assert_close(got_scale, scale, rtol=1e-5, atol=0)
+        out2 = o.linear(rs, w2, torch.empty(M, N2, dtype=torch.bfloat16, device=DEV))
+        want2 = (rs.x.double() * scale) @ w2.double().T          # the kernel sees the rounded gain * resid
+        check(out2, want2, H)
+        results.append((resid.clone(), rs.x.clone(), rs.partials.clone(), out2.clone()))
+        # gated, on the same activations: N2 packed features = N2 / 2 outputs
+        outg = torch.empty(M, N2 // 2, dtype=torch.bfloat16, device=DEV)
+        o.gated_linear(rs, w2, outg, torch.empty(M, N2, dtype=torch.bfloat16, device=DEV), 64)
+        full = want2.view(M, N2 // 128, 2, 64)
+        gd, ud = full[:, :, 0].reshape(M, -1), full[:, :, 1].reshape(M, -1)
+        torch.testing.assert_close(outg.double(), gd / (1 + torch.exp(-gd)) * ud, rtol=2 ** -6, atol=2e-2)
+    torch.cuda.synchronize()
+    o.check_kernel_errors()
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+
+
 def test_strided_rows_and_output():
     x, w, want = case(24, 192, 128, 5, ldx=136, ldw=256)
     wide = torch.zeros(24, 400, dtype=torch.bfloat16, device=DEV)

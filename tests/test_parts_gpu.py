@@ -108,6 +108,47 @@ def test_attention_mixer_alone_over_two_steps(dtype, heads, kv_heads, d, hidden,
     torch.testing.assert_close(torch.cat([y1, y2]).float().cpu(), want, **tol(dtype))
 
 
+def test_blocks_fold_their_norms_into_the_products_of_a_short_step():
+    """Two blocks in bfloat16 on a step of 5 tokens: the products take over the residual sums and the
+    norms (the second block is handed a RowScaled), and stream and output agree with the norm kernels."""
+    from nanospec_b200 import ops
+    from nanospec_b200.config import LayerSpec, PartSpec
+    from nanospec_b200.parts import build_block
+    hidden, heads, kvh, d, inter = 256, 4, 2, 64, 384
+    pos = PartSpec("rope", {"head_dim": d, "theta": 10000.0, "scaling": None})
+    layer = LayerSpec(mixer=PartSpec("gqa_attention", {"hidden": hidden, "heads": heads, "kv_heads": kvh, "head_dim": d,
+                                                       "window": 0, "position": pos}),
+                      feed_forward=PartSpec("swiglu", {"hidden": hidden, "intermediate": inter}),
+                      norm=PartSpec("rmsnorm", {"hidden": hidden, "eps": 1e-5}), prefix="l.", block="prenorm",
+                      names={"mixer": "a.", "feed_forward": "f.", "norm_mixer": "n1.", "norm_feed_forward": "n2."})
+    g = torch.Generator().manual_seed(11)
+    blocks = [build_block(layer, torch.bfloat16, DEV) for _ in range(2)]
+    for b in blocks:
+        for part in b.parts().values():
+            part.bind({n: ((1 + 0.1 * torch.randn(s.shape, generator=g)) if s.init == "gain" else
+                           torch.randn(s.shape, generator=g) * 0.05).to(torch.float32 if s.rule == "float32" else torch.bfloat16).to(DEV)
+                       for n, s in part.weight_specs().items()})
+    need = [(blocks[0].mixer.cache_need(), None)]
+    x0 = torch.randn(5, hidden, generator=g)
+    outs = {}
+    for fuse in (True, False):
+        ops.FUSE_NORM = fuse
+        try:
+            _, ctx = context(torch.bfloat16, need + need, [(0, 5)])
+            resid = x0.clone().to(DEV)
+            resid, pending = blocks[0].forward(resid, None, ctx, ctx.lanes[0], True, follow=blocks[1])
+            assert isinstance(pending, ops.RowScaled) == fuse
+            resid, pending = blocks[1].forward(resid, pending, ctx, ctx.lanes[1], True)
+            assert isinstance(pending, torch.Tensor)
+            outs[fuse] = (resid.clone(), pending.float().clone())
+        finally:
+            ops.FUSE_NORM = True
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    torch.testing.assert_close(outs[True][0], outs[False][0], rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(outs[True][1], outs[False][1], rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_feed_forward_part_alone(dtype):
     from nanospec_b200.config import PartSpec
