@@ -12,8 +12,9 @@
 // the stream (programmatic dependent launch), so the cache streams in while the query is still
 // being rotated.  No block-wide barrier inside the loop: a warp waits for the tile's mbarrier and gives the stage
 // back through another.  At the end the four warps' partial results are combined in shared memory,
-// and the blocks of the cluster combine theirs through distributed shared memory, each block
-// writing one slice of the output in split order - no scratch in global memory, no atomics, and a
+// and the blocks of the cluster combine theirs through distributed shared memory: every block owns
+// one slice of the output, the others store their share of it into its shared memory, and after one
+// cluster barrier it adds them in split order - no scratch in global memory, no atomics, and a
 // result that does not depend on timing.  Launch dimensions do not depend on sequence lengths.
 //
 // Tokens whose request brings more than one token are left to the prefill kernel; padding rows
@@ -62,10 +63,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-    float* part_o = reinterpret_cast<float*>(base_ptr + kDtStages * kStageBytes);  // [16][D], then [16][2]
-    float* part_ml = part_o + 16 * D;
-    const uint32_t part_addr = base + kDtStages * kStageBytes;
-    const uint32_t bar0 = part_addr + (16 * D + 32) * 4;
+    // what the other blocks of the cluster send here: [split][elements of this block's slice], then
+    // [split][16 rows][maximum, sum]
+    float* recv_o = reinterpret_cast<float*>(base_ptr + kDtStages * kStageBytes);
+    float* recv_ml = recv_o + 16 * D + kMaxClusterSplits;
+    const uint32_t recv_o_addr = base + kDtStages * kStageBytes;
+    const uint32_t recv_ml_addr = recv_o_addr + (16 * D + kMaxClusterSplits) * 4;
+    const uint32_t bar0 = recv_ml_addr + kMaxClusterSplits * 32 * 4;
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (kDtStages + s); };
 
@@ -89,6 +93,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int req = token_req[n];
     if (req < 0) return;                                        // the same for every block of the cluster
     if (qo_indptr[req + 1] - qo_indptr[req] != 1) return;
+    // a block's shared memory may be written by the others only once it runs: every block says so here
+    // and checks the others before its first store into them
+    if (n_splits > 1) cluster_arrive();
     const int G = nq / nkv;
     const int h0 = hk * G + ht * 16;
     const int gcount = min(16, G - ht * 16);
@@ -235,8 +242,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     // ---- combine the four warps (each saw a quarter of every tile): the stages are free now -------
     __syncthreads();
-    float* so = reinterpret_cast<float*>(base_ptr);  // [warp][16][D]
-    float* sm = so + kComputeWarps * 16 * D;          // [warp][16] maximum, then [warp][16] sum
+    constexpr int SO = D + 8;                         // padded rows: the warps' stores do not collide
+    float* so = reinterpret_cast<float*>(base_ptr);  // [warp][16][SO]
+    float* sm = so + kComputeWarps * 16 * SO;         // [warp][16] maximum, then [warp][16] sum
     if (warp < kComputeWarps) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -244,12 +252,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         }
         const int r0 = lane >> 2;
-        float* mine = so + (size_t)warp * 16 * D;
+        float* mine = so + (size_t)warp * 16 * SO;
+        if (r0 < gcount) {                            // rows beyond the group hold nothing
 #pragma unroll
-        for (int nb = 0; nb < D / 8; ++nb) {
-            const int col = nb * 8 + 2 * (lane & 3);
-            *reinterpret_cast<float2*>(mine + (size_t)r0 * D + col) = make_float2(o[nb][0], o[nb][1]);
-            *reinterpret_cast<float2*>(mine + (size_t)(r0 + 8) * D + col) = make_float2(o[nb][2], o[nb][3]);
+            for (int nb = 0; nb < D / 8; ++nb)
+                *reinterpret_cast<float2*>(mine + (size_t)r0 * SO + nb * 8 + 2 * (lane & 3)) = make_float2(o[nb][0], o[nb][1]);
+        }
+        if (r0 + 8 < gcount) {
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb)
+                *reinterpret_cast<float2*>(mine + (size_t)(r0 + 8) * SO + nb * 8 + 2 * (lane & 3)) = make_float2(o[nb][2], o[nb][3]);
         }
         if ((lane & 3) == 0) {
             sm[warp * 16 + r0] = m[0];
@@ -259,7 +271,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
     }
     __syncthreads();
-    for (int e = tid; e < gcount * D; e += kDtThreads) {
+    // With several splits every block owns one slice of the output: a block sends each element of its
+    // result to the element's owner (a store into the owner's shared memory), its maxima and sums to all.
+    const int total = gcount * D;
+    const int per = (total + n_splits - 1) / n_splits;  // elements per owner
+    if (n_splits > 1) cluster_wait();                    // every block of the cluster has started
+    for (int e = tid; e < total; e += kDtThreads) {
         const int row = e / D, col = e - row * D;
         float mt = -INFINITY;
 #pragma unroll
@@ -269,48 +286,47 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
             for (int w = 0; w < kComputeWarps; ++w) {
                 const float f = ns_exp2(sm[w * 16 + row] - mt);
-                acc += so[((size_t)w * 16 + row) * D + col] * f;
+                acc += so[((size_t)w * 16 + row) * SO + col] * f;
                 lt += sm[64 + w * 16 + row] * f;
             }
         }
         if (n_splits == 1) {
             out[(size_t)n * o_stride + (size_t)(h0 + row) * D + col] = __float2bfloat16_rn(acc / lt);
         } else {
-            part_o[e] = acc;
+            const int owner = e / per;
+            st_cluster_f32(recv_o_addr + 4u * (uint32_t)(split * per + (e - owner * per)), (uint32_t)owner, acc);
             if (col == 0) {
-                part_ml[row * 2] = mt;
-                part_ml[row * 2 + 1] = lt;
+                for (int r = 0; r < n_splits; ++r) {
+                    st_cluster_f32(recv_ml_addr + 4u * (uint32_t)((split * 16 + row) * 2), (uint32_t)r, mt);
+                    st_cluster_f32(recv_ml_addr + 4u * (uint32_t)((split * 16 + row) * 2 + 1), (uint32_t)r, lt);
+                }
             }
         }
     }
     if (n_splits == 1) return;
 
-    // ---- the blocks of the cluster combine their results: each writes one slice, in split order ----
+    // ---- one cluster barrier, then every block merges its slice from its own shared memory, in split order ----
     cluster_sync();
-    for (int e = split * kDtThreads + tid; e < gcount * D; e += n_splits * kDtThreads) {
+    for (int i = tid; i < per && split * per + i < total; i += kDtThreads) {
+        const int e = split * per + i;
         const int row = e / D;
-        // every split's maximum, sum and partial value are requested together
-        float ms[kMaxClusterSplits], ls[kMaxClusterSplits], os[kMaxClusterSplits];
-#pragma unroll
-        for (int s2 = 0; s2 < kMaxClusterSplits; ++s2) {
-            const bool on = s2 < n_splits;
-            ms[s2] = on ? ld_cluster_f32(part_addr + 4u * (uint32_t)(16 * D + row * 2), (uint32_t)s2) : -INFINITY;
-            ls[s2] = on ? ld_cluster_f32(part_addr + 4u * (uint32_t)(16 * D + row * 2 + 1), (uint32_t)s2) : 0.f;
-            os[s2] = on ? ld_cluster_f32(part_addr + 4u * (uint32_t)e, (uint32_t)s2) : 0.f;
-        }
         float mt = -INFINITY;
 #pragma unroll
-        for (int s2 = 0; s2 < kMaxClusterSplits; ++s2) mt = fmaxf(mt, ms[s2]);
+        for (int s2 = 0; s2 < kMaxClusterSplits; ++s2)
+            if (s2 < n_splits) mt = fmaxf(mt, recv_ml[(s2 * 16 + row) * 2]);
         float acc = 0.f, lt = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < kMaxClusterSplits; ++s2) {
-            const float f = ms[s2] == -INFINITY ? 0.f : ns_exp2(ms[s2] - mt);  // an empty split adds nothing
-            acc += os[s2] * f;
-            lt += ls[s2] * f;
+            if (s2 < n_splits) {
+                const float ms = recv_ml[(s2 * 16 + row) * 2];
+                const float f = ms == -INFINITY ? 0.f : ns_exp2(ms - mt);  // an empty split adds nothing
+                acc += recv_o[s2 * per + i] * f;
+                lt += recv_ml[(s2 * 16 + row) * 2 + 1] * f;
+            }
         }
         out[(size_t)n * o_stride + (size_t)h0 * D + e] = __float2bfloat16_rn(acc / lt);
     }
-    cluster_sync();  // no block may exit while another still reads its shared memory
+    // nothing reads another block's shared memory after the barrier: a block may exit when it is done
 }
 
 template <int D>
@@ -318,8 +334,8 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                       int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                       int o_stride, const int* rows, int n_tokens, int nq, int nkv, int page_size, float scale, int window,
                       int n_splits, int* error_flag, cudaStream_t stream) {
-    constexpr int kSmem = kDtStages * 2 * kKeys * D * 2 + (16 * D + 32) * 4 + 2 * kDtStages * 8 + 1024;
-    static_assert(kDtStages * 2 * kKeys * D * 2 >= (kComputeWarps * 16 * D + 128) * 4, "the warps' partial results reuse the stages");
+    constexpr int kSmem = kDtStages * 2 * kKeys * D * 2 + (16 * D + kMaxClusterSplits + kMaxClusterSplits * 32) * 4 + 2 * kDtStages * 8 + 1024;
+    static_assert(kDtStages * 2 * kKeys * D * 2 >= (kComputeWarps * 16 * (D + 8) + 128) * 4, "the warps' partial results reuse the stages");
     static bool configured = false;
     if (!configured) {
         NS_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));

@@ -167,6 +167,8 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // a float from the shared memory of block `rank` of this cluster, at the address that `local` has here
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local, uint32_t rank) {
     uint32_t remote;
@@ -174,6 +176,13 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
     return v;
+}
+
+// a float into the shared memory of block `rank` of this cluster, at the address that `local` has here
+__device__ __forceinline__ void st_cluster_f32(uint32_t local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 // ---- tensor maps (host) ------------------------------------------------------------------------
