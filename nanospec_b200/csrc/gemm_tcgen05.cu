@@ -21,7 +21,7 @@
 // Gated mode (the feed-forward's packed projection): the weight rows alternate between 64 gate and
 // 64 up features, so a block's tile holds both halves of 64 outputs and the epilogue writes
 // silu(gate) * up - the activation costs no kernel and no trip through global memory.
-// Two more epilogues let a decode step do without its norm kernels (16 tokens at most):
+// Two more epilogues let a decode step do without its norm kernels (64 tokens at most):
 //   sink:  the output is a branch of the residual stream that an RMSNorm follows.  The block adds
 //          its features to the fp32 residual, writes gain * residual in bf16 for the next product and
 //          the sum of squares of its features per token; the norm's scale, one number per token, is
@@ -63,7 +63,8 @@ enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kE
 template <int BN>
 struct Cfg {
     // up to 64 tokens: stages sized so that two blocks share an SM (8 to 12 tiles in flight per SM)
-    static constexpr int kStages = BN <= 32 ? 6 : (BN == 64 ? 4 : (BN == 128 ? 6 : 4));
+    // up to 64 tokens: stages sized so that two blocks share an SM
+    static constexpr int kStages = BN == 16 ? 6 : BN == 32 ? 5 : (BN == 64 ? 4 : (BN == 128 ? 6 : 4));
     static constexpr int kMinBlocks = BN <= 64 ? 2 : 1;
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
@@ -89,8 +90,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int gated = ep.gated;
     const bool sink = ep.sink_resid != nullptr;
     // per-token scale (scale mode) and squares of the finished residual (sink mode); both modes are
-    // offered for tiles of 16 tokens only
-    __shared__ float inv_s[16];
+    // offered for tiles of up to 64 tokens
+    constexpr bool kNorm = BN <= 64;
+    __shared__ float inv_s[kNorm ? BN : 1];
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -103,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ int failed;
     // after the last MMA the pipeline stages are free: the split-K partial tile is staged there
     float* stage_f32 = reinterpret_cast<float*>(smem_dyn + (base - smem_u32(smem_dyn)));
-    float* sq_s = stage_f32 + BN * BM;  // sink mode (16 tokens): [16][BM + 1] squares, behind the partial tile
+    float* sq_s = stage_f32 + BN * BM;  // sink mode: [BN][BM + 1] squares, behind the partial tile
 
     ns_pdl_launch_dependents();  // the next kernel may be scheduled; it waits for this one before it reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,9 +192,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ns_pdl_wait();           // before anything is written that the previous kernel may still read
         const int q = warp & 3;  // the TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;
-        if (BN == 16) {
+        if (kNorm) {
             // while the products run: each token's scale, one warp per token, partial sums in ascending order
-            for (int t = warp - 2; t < 16; t += 4) {
+            for (int t = warp - 2; t < BN; t += 4) {
                 float inv = 1.f;
                 if (ep.row_partials && tok0 + t < M_tok) {
                     const float* p = ep.row_partials + (size_t)(tok0 + t) * ep.n_partials;
@@ -224,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int tok = tok0 + c * 8 + j;
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
-                            if (splits == 1 && !gated && !sink) store_out(out + (size_t)tok * ldo + f, BN == 16 ? v * inv_s[c * 8 + j] : v);
+                            if (splits == 1 && !gated && !sink) store_out(out + (size_t)tok * ldo + f, kNorm ? v * inv_s[c * 8 + j] : v);
                             else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
@@ -267,8 +269,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float acc = 0.f;
 #pragma unroll
                 for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
-                if (BN == 16) acc *= inv_s[j];
-                if (BN == 16 && sink) {
+                if (kNorm) acc *= inv_s[j];
+                if (kNorm && sink) {
                     const size_t o = (size_t)(tok0 + j) * ep.sink_ld + n0 + i;
                     const float r = ep.sink_resid[o] + acc;
                     ep.sink_resid[o] = r;
@@ -278,7 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
                 }
             }
-            if (BN == 16 && sink) {
+            if (kNorm && sink) {
                 // the block's share of each token's sum of squares, added in feature order
                 __syncthreads();
                 if ((int)threadIdx.x < tok_n) {
@@ -305,7 +307,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float gs = 0.f, us = 0.f;
 #pragma unroll
                 for (int s = 0; s < kMaxSplits; ++s) { gs += g[s]; us += u[s]; }
-                if (BN == 16) { gs *= inv_s[j]; us *= inv_s[j]; }
+                if (kNorm) { gs *= inv_s[j]; us *= inv_s[j]; }
                 store_out(out + (size_t)(tok0 + j) * ldo + o0 + i, (gs / (1.f + expf(-gs))) * us);
             }
         }
@@ -379,8 +381,8 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: no error flag");
     int bn, bm;
     ns_gemm_bf16_tc_tile(M_tok, &bn, &bm);
-    if ((ep.row_partials || ep.sink_resid) && bn != 16)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: the norm epilogues take 16 tokens at most, not %d", M_tok);
+    if ((ep.row_partials || ep.sink_resid) && bn > 64)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: the norm epilogues take 64 tokens at most, not %d", M_tok);
     if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || !ep.sink_partials))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink needs %d features to be a multiple of %d, and all its tensors", N_feat, BM);
     if (ep.row_partials && ep.n_partials < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: n_partials=%d", ep.n_partials);
@@ -419,7 +421,7 @@ NS_API int ns_gemm_bf16_tc_gated(const void* x, const void* w, void* out, int M_
     return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
 }
 
-// The same products with the norm epilogues (16 tokens at most).
+// The same products with the norm epilogues (64 tokens at most).
 //   row_partials [M_tok, n_partials] (or null): every output row is multiplied by
 //       rsqrt(sum of the row's partials / hidden + eps) - the activations x were left unscaled by a sink;
 //   sink_resid [M_tok, sink_ld] (or null; not with gated): the product is added to it, sink_x [M_tok, sink_ld] gets

@@ -111,7 +111,16 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
     }
 }
 
+int g_token_kernel_from = 128;  // measured in a decode step of 32 and of 64 tokens: a block per (token, head) is ahead there
+
 }  // namespace
+
+// Steps with at least this many tokens take the kernel with one block per token (default 128).
+NS_API int ns_rope_token_kernel_from(int n_tokens) {
+    if (n_tokens < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_rope_token_kernel_from: %d", n_tokens);
+    g_token_kernel_from = n_tokens;
+    return NS_OK;
+}
 
 // rot_pairs = number of (j, j + d/2) pairs that are rotated (d/2 for full rotary).
 NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_req, const int* block_table,
@@ -122,7 +131,7 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
     if (d % 2 || rot_pairs > d / 2 || rot_pairs < 0)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_rope_kv_write: head_dim=%d rot_pairs=%d (head_dim must be even, pairs <= head_dim/2)", d, rot_pairs);
     if (nq + 2 * nkv > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_rope_kv_write: %d heads exceed the grid", nq + 2 * nkv);
-    if (n_tokens >= 64 && 2 * (size_t)rot_pairs * sizeof(float) <= 48 * 1024) {
+    if (n_tokens >= g_token_kernel_from && 2 * (size_t)rot_pairs * sizeof(float) <= 48 * 1024) {
         const size_t smem = 2 * (size_t)rot_pairs * sizeof(float);
         if (dtype == NS_F32)
             NS_LAUNCH((rope_kv_write_token_kernel<float>), n_tokens, 256, smem, stream, (float*)qkv, positions, token_req,

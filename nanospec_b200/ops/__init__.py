@@ -115,9 +115,10 @@ _tc_state: dict[torch.device, _TensorCoreGemmState] = {}
 _SM_COUNT = 148
 USE_TENSOR_CORE_GEMM = True  # the hand-written tcgen05 kernel; False hands every bf16 product to cuBLAS
 # Products with more tokens than this go to cuBLAS, whose kernels are ahead of the hand-written
-# one there (measured: 68-85 % of cuBLAS at 2,048 tokens, behind it at 64 because of split-K
-# traffic); None = no limit.
-TENSOR_CORE_GEMM_MAX_TOKENS: int | None = 16
+# one there (measured in decode steps of the 8B shape: with 32 tokens the hand-written kernel and its
+# fused epilogues take 3.98 ms against 4.40 ms, with 64 tokens 5.44 ms against 4.9-5.0 ms; at 2,048
+# tokens it reaches 68-85 % of cuBLAS); None = no limit.
+TENSOR_CORE_GEMM_MAX_TOKENS: int | None = 32
 
 
 def _tc(device: torch.device) -> _TensorCoreGemmState:
@@ -216,9 +217,9 @@ def _tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def norm_fusion_ok(n_tokens: int, dtype: torch.dtype, *weights: torch.Tensor) -> bool:
     """Whether a step of `n_tokens` in `dtype` may hand normed activations on as `RowScaled` to products
-    with these weights (and fold a norm into a product with them): the tcgen05 kernel with a tile of 16
+    with these weights (and fold a norm into a product with them): the tcgen05 kernel with a tile of up to 64
     tokens, feature counts in multiples of 128, rows that TMA can address."""
-    if not (FUSE_NORM and USE_TENSOR_CORE_GEMM and dtype == torch.bfloat16 and 0 < n_tokens <= 16):
+    if not (FUSE_NORM and USE_TENSOR_CORE_GEMM and dtype == torch.bfloat16 and 0 < n_tokens <= 64):
         return False
     if TENSOR_CORE_GEMM_MAX_TOKENS is not None and n_tokens > TENSOR_CORE_GEMM_MAX_TOKENS:
         return False
@@ -233,7 +234,7 @@ def _linear_norm(x, w: torch.Tensor, out: torch.Tensor | None, gated: bool, sink
     xt = scaled.x if scaled is not None else x
     M, K = xt.shape
     N = w.shape[0]
-    if w.shape[1] != K or not _tma_ok(xt, w) or M > 16:
+    if w.shape[1] != K or not _tma_ok(xt, w) or M > 64:
         raise KernelError(f"linear: the norm epilogues cannot take x {tuple(xt.shape)}, w {tuple(w.shape)}")
     splits = gemm_splits(M, N, K)
     res = None
