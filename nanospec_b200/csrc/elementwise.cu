@@ -107,28 +107,6 @@ add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, cons
 
 // Vector variant for widths that are a multiple of 8 with 16-byte aligned rows: every thread owns
 // CHUNKS groups of 8 consecutive elements, read and written with 16-byte accesses.
-__device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
-}
-__device__ __forceinline__ void st8(float* p, const float (&v)[8]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) {
-    uint4 u;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = u;
-}
-
 template <typename T, int THREADS, int CHUNKS>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
@@ -252,6 +230,13 @@ NS_API int ns_residual_add(float* resid, const void* branch, int n_rows, int hid
 // SwiGLU gate on the packed [gate | up] projection:
 //   out[n, j] = silu(gu[n, j]) * gu[n, inter + j],  silu(a) = a / (1 + exp(-a)),  in float
 // ---------------------------------------------------------------------------------------
+// silu(g) * u.  The float kernels use the accurate exponential and division; the bfloat16 ones the
+// hardware approximations (about 2 ulp in float, far below the rounding of the result).
+template <typename T>
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.f + expf(-g))) * u; }
+template <>
+__device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
@@ -264,7 +249,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     const size_t gi = block ? (size_t)(j / block) * 2 * block + j % block : (size_t)j;
     const float g = ns_ld(gu, n * 2 * (size_t)inter + gi);
     const float u = ns_ld(gu, n * 2 * (size_t)inter + gi + (block ? block : inter));
-    ns_st(out, i, (g / (1.f + expf(-g))) * u);
+    ns_st(out, i, silu_mul<T>(g, u));
 }
 
 template <typename T>
@@ -281,7 +266,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out,
     ld8(gu + n * 2 * (size_t)inter + gi, g);
     ld8(gu + n * 2 * (size_t)inter + gi + (block ? block : inter), u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) y[k] = (g[k] / (1.f + expf(-g[k]))) * u[k];
+    for (int k = 0; k < 8; ++k) y[k] = silu_mul<T>(g[k], u[k]);
     st8(out + n * (size_t)inter + j, y);
 }
 

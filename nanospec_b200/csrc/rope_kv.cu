@@ -59,7 +59,7 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
 // The same work with one block per token (all heads), for steps with many tokens: a block per
 // (token, head) would then be bound by the rate at which blocks can be scheduled.  cos and sin of
 // the token's angles are computed once and shared through shared memory.
-template <typename T>
+template <typename T, bool kVec>
 __global__ void __launch_bounds__(256)
 rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_req,
                            const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq,
@@ -88,6 +88,41 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
     }
     const size_t head_stride = (size_t)page_size * d;                   // from one kv head to the next
     const int rot_heads = write_kv ? nq + nkv : nq;
+    if (kVec) {
+        // half a head is a multiple of 8 elements and every row is 16-byte aligned: 8 pairs per thread and turn
+        const int per_head = half / 8;
+        for (int i = threadIdx.x; i < rot_heads * per_head; i += blockDim.x) {
+            const int h = i / per_head, j = (i - h * per_head) * 8;
+            T* x = row + (size_t)h * d;
+            float x1[8], x2[8], o1[8], o2[8];
+            ld8(x + j, x1);
+            ld8(x + j + half, x2);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                o1[u] = x1[u];
+                o2[u] = x2[u];
+                if (j + u < rot_pairs) {
+                    const float c = cs[j + u], s = cs[rot_pairs + j + u];
+                    o1[u] = __fmaf_rn(x1[u], c, -__fmul_rn(x2[u], s));
+                    o2[u] = __fmaf_rn(x2[u], c, __fmul_rn(x1[u], s));
+                }
+            }
+            T* dst = h < nq ? x : k_cache + base + (size_t)(h - nq) * head_stride;
+            st8(dst + j, o1);
+            st8(dst + j + half, o2);
+        }
+        if (write_kv) {
+            const T* v = row + (size_t)(nq + nkv) * d;
+            const int per_v = d / 8;
+            for (int i = threadIdx.x; i < nkv * per_v; i += blockDim.x) {
+                const int hk = i / per_v, e = (i - hk * per_v) * 8;
+                float t[8];
+                ld8(v + (size_t)hk * d + e, t);
+                st8(v_cache + base + (size_t)hk * head_stride + e, t);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
         const int h = i / half, j = i - h * half;
         T* x = row + (size_t)h * d;
@@ -133,12 +168,24 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
     if (nq + 2 * nkv > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_rope_kv_write: %d heads exceed the grid", nq + 2 * nkv);
     if (n_tokens >= g_token_kernel_from && 2 * (size_t)rot_pairs * sizeof(float) <= 48 * 1024) {
         const size_t smem = 2 * (size_t)rot_pairs * sizeof(float);
-        if (dtype == NS_F32)
-            NS_LAUNCH((rope_kv_write_token_kernel<float>), n_tokens, 256, smem, stream, (float*)qkv, positions, token_req,
+        // 16-byte accesses when half a head is a multiple of 8 elements and the tensors are 16-byte aligned
+        // (rows of qkv and of the cache are then aligned too); the arithmetic is the same either way
+        const bool vec = d % 16 == 0 && (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0) &&
+                         (dtype == NS_F32 || dtype == NS_BF16);
+        if (dtype == NS_F32 && vec)
+            NS_LAUNCH((rope_kv_write_token_kernel<float, true>), n_tokens, 256, smem, stream, (float*)qkv, positions, token_req,
+                      block_table, table_stride, inv_freq, (float*)k_cache, (float*)v_cache, page_size, nq, nkv, d,
+                      rot_pairs, write_kv);
+        else if (dtype == NS_BF16 && vec)
+            NS_LAUNCH((rope_kv_write_token_kernel<__nv_bfloat16, true>), n_tokens, 256, smem, stream, (__nv_bfloat16*)qkv,
+                      positions, token_req, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache,
+                      (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, rot_pairs, write_kv);
+        else if (dtype == NS_F32)
+            NS_LAUNCH((rope_kv_write_token_kernel<float, false>), n_tokens, 256, smem, stream, (float*)qkv, positions, token_req,
                       block_table, table_stride, inv_freq, (float*)k_cache, (float*)v_cache, page_size, nq, nkv, d,
                       rot_pairs, write_kv);
         else if (dtype == NS_BF16)
-            NS_LAUNCH((rope_kv_write_token_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (__nv_bfloat16*)qkv,
+            NS_LAUNCH((rope_kv_write_token_kernel<__nv_bfloat16, false>), n_tokens, 256, smem, stream, (__nv_bfloat16*)qkv,
                       positions, token_req, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, rot_pairs, write_kv);
         else
