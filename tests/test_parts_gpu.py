@@ -343,3 +343,142 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             top = z.topk(2).values
             assert t == int(z.argmax()) or float(top[0] - top[1]) < 1e-5
             ids.append(t)
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
+    """Two more parts defined here and registered from outside the package: a feed-forward that routes every
+    token to one of three experts (router logits in float32), and a position encoding that rotates interleaved
+    pairs (2i, 2i+1) instead of halves.  A model folder that names them is written, loaded, stepped in
+    portions beside another request, and compared with a plain statement of the same arithmetic."""
+    from nanospec_b200 import ops
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.config import Architecture, LlamaConfig, PartSpec, register_architecture
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.parts import Part, WeightSpec, register_part
+    from nanospec_b200.weights import load_model, write_random_model
+    import dataclasses
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class Top1Experts(Part):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.hidden, self.inter, self.experts = spec["hidden"], spec["intermediate"], spec["experts"]
+
+        def weight_specs(self):
+            specs = {"router.weight": WeightSpec((self.experts, self.hidden), rule="float32", std=0.5)}
+            for e in range(self.experts):
+                specs[f"experts.{e}.up.weight"] = WeightSpec((self.inter, self.hidden), std=0.1)
+                specs[f"experts.{e}.down.weight"] = WeightSpec((self.hidden, self.inter), std=0.1)
+            return specs
+
+        def bind(self, tensors):
+            self.w = tensors
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.w["router.weight"].T          # router logits in float32
+            prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = ctx.buffer("branch", self.hidden)
+            out.zero_()
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(x[rows] @ self.w[f"experts.{e}.up.weight"].T)
+                    y = (h @ self.w[f"experts.{e}.down.weight"].T).float() * prob[rows, None]
+                    out[rows] = y.to(out.dtype)
+            return out
+
+    @register_part("position", "toy_interleaved_rotary")
+    class InterleavedRotary(Part):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            d = spec["head_dim"]
+            self.freq = (1.0 / (spec["theta"] ** (torch.arange(0, d, 2).float() / d))).to(device)
+
+        def rotate_and_store(self, qkv, ctx, lane, nq, nkv, head_dim, writes):
+            ang = ctx.positions.float()[:, None] * self.freq[None, :]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            qk = qkv[:, : (nq + nkv) * head_dim].view(-1, nq + nkv, head_dim // 2, 2).float()
+            a, b = qk[..., 0], qk[..., 1]
+            rot = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1)
+            qkv[:, : (nq + nkv) * head_dim] = rot.reshape(qkv.shape[0], -1).to(qkv.dtype)
+            if writes:
+                ops.kv_store(qkv, ctx, lane, nq, nkv, head_dim)
+
+    heads, kvh, d, hidden, inter, experts = 4, 2, 16, 48, 40, 3
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        mixer = r.layers[0].mixer
+        toy_pos = PartSpec("toy_interleaved_rotary", {"head_dim": d, "theta": 100.0})
+        l0 = dataclasses.replace(r.layers[0], mixer=PartSpec(mixer.kind, {**mixer.params, "position": toy_pos}))
+        l1 = dataclasses.replace(r.layers[1], feed_forward=PartSpec("toy_top1_experts", {"hidden": hidden, "intermediate": inter,
+                                                                                         "experts": experts}),
+                                 names={**r.layers[1].names, "feed_forward": "moe."})
+        return dataclasses.replace(r, architecture="ToyRoutedForCausalLM", layers=(l0, l1))
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", "toy-routed-test", LlamaConfig.from_hf, recipe))
+    cfg = LlamaConfig(vocab_size=90, hidden_size=hidden, intermediate_size=64, num_hidden_layers=2, num_attention_heads=heads,
+                      num_key_value_heads=kvh, head_dim=d, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=64)
+    hf = cfg.to_hf()
+    hf["architectures"] = ["ToyRoutedForCausalLM"]
+    write_random_model(tmp_path, hf, seed=9)
+    pcfg, w = plain.read_folder(tmp_path)
+    assert "model.layers.1.moe.experts.2.down.weight" in w and w["model.layers.1.moe.router.weight"].dtype == torch.float32
+    model = load_model(tmp_path, device="cuda", dtype=torch.float32)
+
+    def plain_logits(ids):
+        S = len(ids)
+        positions = torch.arange(S)
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)].float()
+        # layer 0: attention with interleaved rotary, the usual feed-forward
+        p = "model.layers.0."
+        h = plain.plain_rmsnorm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+        q = (h @ w[p + "self_attn.q_proj.weight"].float().T).view(S, heads, d)
+        k = (h @ w[p + "self_attn.k_proj.weight"].float().T).view(S, kvh, d)
+        v = (h @ w[p + "self_attn.v_proj.weight"].float().T).view(S, kvh, d)
+        ang = positions.float()[:, None] * (1.0 / (100.0 ** (torch.arange(0, d, 2).float() / d)))[None, :]
+
+        def rot(t):
+            a, b = t[..., 0::2], t[..., 1::2]
+            c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            return torch.stack([a * c - b * s, b * c + a * s], dim=-1).reshape(t.shape)
+
+        att = plain.plain_attention(rot(q), rot(k), v).reshape(S, heads * d)
+        x = x + att @ w[p + "self_attn.o_proj.weight"].float().T
+        x = x + plain.plain_mlp(plain.plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"]), w, p + "mlp.")
+        # layer 1: the usual attention, the routed feed-forward
+        p = "model.layers.1."
+        h = plain.plain_rmsnorm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+        x = x + plain.plain_attention_block(h, w, p + "self_attn.", {"heads": heads, "kv_heads": kvh, "head_dim": d}, positions,
+                                            plain.plain_inv_freq(d, 10000.0, None))
+        h = plain.plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"])
+        prob, choice = torch.softmax(h @ w[p + "moe.router.weight"].T, dim=-1).max(dim=-1)
+        y = torch.zeros_like(x)
+        for e in range(experts):
+            rows = (choice == e).nonzero().flatten()
+            up, down = w[p + f"moe.experts.{e}.up.weight"].float(), w[p + f"moe.experts.{e}.down.weight"].float()
+            y[rows] = (torch.relu(h[rows] @ up.T) @ down.T) * prob[rows, None]
+        x = x + y
+        return plain.plain_rmsnorm(x, w["model.norm.weight"], pcfg["eps"]) @ w["lm_head.weight"].float().T, choice
+
+    seqs = {0: random_ids(27, 90, seed=4), 1: random_ids(15, 90, seed=5)}
+    runner = ModelRunner(model, num_blocks=24, block_size=4, max_requests=2)
+    got = {r: [] for r in seqs}
+
+    def run(entries):
+        out = runner.step([StepEntry(r, seqs[r][a:b], list(range(b - a))) for r, a, b in entries])
+        row = 0
+        for r, a, b in entries:
+            got[r].append(out[row: row + b - a].float().cpu())
+            row += b - a
+
+    runner.begin(0), runner.begin(1)
+    run([(0, 0, 9), (1, 0, 2)])
+    run([(1, 2, 3), (0, 9, 11)])
+    run([(0, 11, 27), (1, 3, 15)])
+    runner.end(0), runner.end(1)
+    runner.manager.check()
+    for r, ids in seqs.items():
+        want, choice = plain_logits(ids)
+        assert len(set(choice.tolist())) > 1  # the router really sends tokens to different experts
+        torch.testing.assert_close(torch.cat(got[r]), want, rtol=3e-5, atol=3e-6)
