@@ -125,8 +125,10 @@ def cmd_bench(args) -> int:
 
 
 def cmd_profile(args) -> int:
-    """One decode step or one prefill step at a named shape with random weights, bracketed by
-    cudaProfilerStart/Stop so that a profiler started with --profile-from-start off sees only it."""
+    """Decode steps, or the prefill of one batch of prompts, at a named shape with random weights,
+    bracketed by cudaProfilerStart/Stop so that a profiler started with --profile-from-start off sees
+    only them.  Prints the median step time, tokens per second and (decode) the bytes a step has to
+    read over its time."""
     import torch
 
     from .config import Llama3RopeScaling, LlamaConfig
@@ -150,12 +152,13 @@ def cmd_profile(args) -> int:
     model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
     args.max_running = max(args.batch, 1)
     args.max_admit = 64
-    pages = args.batch * (-(-(args.context + 256) // args.block_size) + 1) + 8
+    pages = (args.batch + (1 if args.what == "prefill" else 0)) * (-(-(args.context + 256 + args.steps) // args.block_size) + 1) + 8
     engine = _engine(model, args, pages)
     g = torch.Generator().manual_seed(0)
     n_prompt = args.context - 1 if args.what == "decode" else args.context
     reqs = [engine.add(torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist(),
-                       SamplingParams(max_tokens=256 if args.what == "decode" else 1, ignore_eos=True)) for _ in range(args.batch)]
+                       SamplingParams(max_tokens=256 + args.steps if args.what == "decode" else 1, ignore_eos=True))
+            for _ in range(args.batch)]
     if args.what == "decode":
         while any(r.state == "waiting" or (r.state == "running" and r.pending > 1) for r in reqs):
             engine.step()
@@ -167,18 +170,43 @@ def cmd_profile(args) -> int:
         engine.sched.waiting.remove(warm)
         engine.sched.waiting.appendleft(warm)
         engine.sched.max_admit = 1
-        engine.step()
+        while warm.state != "done":   # a prompt longer than a portion takes several steps
+            engine.step()
         engine.sched.max_admit = 64
     torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
     torch.cuda.profiler.start()
-    a.record()
-    engine.step()
-    b.record()
+    if args.what == "decode":
+        for _ in range(args.steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            engine.step()
+            b.record()
+            times.append((a, b))
+    else:
+        while any(r.state != "done" for r in reqs):   # every portion of every prompt
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            engine.step()
+            b.record()
+            times.append((a, b))
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
-    print(json.dumps({"what": args.what, "shape": args.shape, "layers": layers, "batch": args.batch, "context": args.context,
-                      "graphs": not args.no_cuda_graphs, "step_ms": round(a.elapsed_time(b), 3)}), flush=True)
+    ms = sorted(a.elapsed_time(b) for a, b in times)
+    out = {"what": args.what, "shape": args.shape, "layers": layers, "batch": args.batch, "context": args.context,
+           "graphs": not args.no_cuda_graphs, "steps": len(ms), "step_ms": round(ms[len(ms) // 2], 3)}
+    if args.what == "decode":
+        per_layer = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim * cfg.hidden_size \
+            + cfg.hidden_size * cfg.num_attention_heads * cfg.head_dim + 3 * cfg.intermediate_size * cfg.hidden_size
+        elt = 2 if args.dtype == "bfloat16" else 4
+        step_bytes = elt * (layers * per_layer + cfg.vocab_size * cfg.hidden_size) \
+            + args.batch * args.context * 2 * layers * cfg.num_key_value_heads * cfg.head_dim * elt
+        out["tokens_per_s"] = round(args.batch * 1000.0 / out["step_ms"], 1)
+        out["gb_per_s"] = round(step_bytes / (out["step_ms"] * 1e-3) / 1e9, 1)
+    else:
+        out["total_ms"] = round(sum(ms), 3)
+        out["tokens_per_s"] = round(args.batch * args.context * 1000.0 / sum(ms), 1)
+    print(json.dumps(out), flush=True)
     return 0
 
 
@@ -240,6 +268,7 @@ def main(argv: list[str] | None = None) -> int:
     pr.add_argument("--batch", type=int, default=8)
     pr.add_argument("--context", type=int, default=1024)
     pr.add_argument("--what", choices=["decode", "prefill"], default="decode")
+    pr.add_argument("--steps", type=int, default=1, help="decode steps to time (the median is printed)")
     pr.set_defaults(fn=cmd_profile)
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
