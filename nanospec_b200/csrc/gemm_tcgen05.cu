@@ -26,6 +26,9 @@
 //          its features to the fp32 residual, writes gain * residual in bf16 for the next product and
 //          the sum of squares of its features per token; the norm's scale, one number per token, is
 //          still missing from those activations.
+//   rope:  the product is the packed q/k/v projection: the epilogue rotates q and k by the token's position
+//          and writes k and v straight to the token's cache slot - no rotation kernel, and k and v never
+//          travel through the projection's output buffer.
 //   scale: the activations came from such a sink.  The epilogue adds up the partial sums of squares of
 //          each token (in a fixed order), and multiplies the token's outputs by
 //          rsqrt(sum / hidden + eps) - a product is linear in a per-token scale of its input.
@@ -56,6 +59,16 @@ struct GemmEpilogue {
     __nv_bfloat16* sink_x;        // [tokens, sink_ld]
     float* sink_partials;         // [tokens, feature tiles * splits]
     int sink_ld;
+    // rope: the product is an attention layer's packed [q | k | v] projection.  q and k are rotated by the
+    // token's position (pairs (j, j + head_dim / 2)); q goes to `out`, k and v to the token's slot of the cache
+    // [page, kv head, offset, head_dim].  Tiles of 128 features hold whole heads (head_dim 32, 64 or 128).
+    const int* rope_positions;    // [tokens]; null: no rope epilogue
+    const int* rope_token_req;    // [tokens], negative: a padding row
+    const int* rope_block_table;  // [requests, rope_table_stride]
+    const float* rope_inv_freq;   // [rope_pairs]
+    __nv_bfloat16* rope_k_cache;
+    __nv_bfloat16* rope_v_cache;
+    int rope_table_stride, rope_page_size, rope_nq, rope_nkv, rope_head_dim, rope_pairs, rope_write_kv;
 };
 
 enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrDrainWait = 4 };
@@ -89,6 +102,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                int* __restrict__ error_flag) {
     const int gated = ep.gated;
     const bool sink = ep.sink_resid != nullptr;
+    const bool rope = ep.rope_positions != nullptr;
     // per-token scale (scale mode) and squares of the finished residual (sink mode); both modes are
     // offered for tiles of up to 64 tokens
     constexpr bool kNorm = BN <= 64;
@@ -117,6 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int kb_begin = split * per + min(split, rem);
     const int kb_count = per + (split < rem ? 1 : 0);
 
+    float rope_sin0 = 0.f, rope_cos0 = 1.f;  // rope mode: sine and cosine of a thread's first (token, pair)
     if (threadIdx.x == 0) {
         failed = 0;
         for (int s = 0; s < C::kStages; ++s) {
@@ -206,6 +221,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         }
+        if (kNorm && rope) {
+            // this thread's first (token, pair) of the reduction below: its angle does not wait for the product
+            const int npid = (BM / 2) / splits;
+            const int e = (int)threadIdx.x - 64;
+            const int tok_n = min(BN, M_tok - tok0);
+            if (e < tok_n * npid) {
+                const int j = e / npid, pid = split * npid + (e - j * npid);
+                const int p = pid % (ep.rope_head_dim / 2);
+                if (p < ep.rope_pairs) sincosf((float)ep.rope_positions[tok0 + j] * ep.rope_inv_freq[p], &rope_sin0, &rope_cos0);
+            }
+        }
         bool ok = true;
         if (lane == 0) ok = mbar_wait(accum_bar, 0);
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -226,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int tok = tok0 + c * 8 + j;
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
-                            if (splits == 1 && !gated && !sink) store_out(out + (size_t)tok * ldo + f, kNorm ? v * inv_s[c * 8 + j] : v);
+                            if (splits == 1 && !gated && !sink && !rope) store_out(out + (size_t)tok * ldo + f, kNorm ? v * inv_s[c * 8 + j] : v);
                             else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
@@ -242,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
-    if (splits == 1 && !gated && !sink) return;
+    if (splits == 1 && !gated && !sink && !rope) return;
 
     // The `splits` blocks of one output tile form a thread-block cluster.  Each has left its fp32
     // partial tile in its own shared memory; after a cluster barrier every block adds, in rank
@@ -257,7 +283,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     };
     if (!failed) {
         const int tok_n = min(BN, M_tok - tok0);
-        if (!gated) {
+        if (kNorm && rope) {
+            // Pairs (j, j + head_dim / 2) of a head are rotated together: this block finishes 64 / splits pairs
+            // per token, both members of each.  The four epilogue warps do it (they hold the first angles).
+            const int D = ep.rope_head_dim, half = D / 2;
+            const int npid = (BM / 2) / splits;
+            for (int e = (int)threadIdx.x - 64; e >= 0 && e < tok_n * npid; e += 128) {
+                const int j = e / npid, pid = split * npid + (e - j * npid);
+                const int head_local = pid / half, p = pid - head_local * half;
+                const int lo = head_local * D + p, hi = lo + half;       // features within the tile
+                const int tok = tok0 + j;
+                const int req = ep.rope_token_req[tok];
+                if (req < 0 || n0 + hi >= N_feat) continue;
+                float a[kMaxSplits], b[kMaxSplits];
+#pragma unroll
+                for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+                    a[s2] = s2 < splits ? partial(j * BM + lo, s2) : 0.f;
+                    b[s2] = s2 < splits ? partial(j * BM + hi, s2) : 0.f;
+                }
+                float x1 = 0.f, x2 = 0.f;
+#pragma unroll
+                for (int s2 = 0; s2 < kMaxSplits; ++s2) { x1 += a[s2]; x2 += b[s2]; }
+                x1 *= inv_s[j];
+                x2 *= inv_s[j];
+                const int gh = n0 / D + head_local;                     // head among [q | k | v]
+                const int pos = ep.rope_positions[tok];
+                float o1 = x1, o2 = x2;
+                if (gh < ep.rope_nq + ep.rope_nkv && p < ep.rope_pairs) {
+                    float sn = rope_sin0, cs = rope_cos0;
+                    if (e != (int)threadIdx.x - 64) sincosf((float)pos * ep.rope_inv_freq[p], &sn, &cs);
+                    o1 = __fmaf_rn(x1, cs, -__fmul_rn(x2, sn));
+                    o2 = __fmaf_rn(x2, cs, __fmul_rn(x1, sn));
+                }
+                if (gh < ep.rope_nq) {
+                    store_out(out + (size_t)tok * ldo + (size_t)gh * D + p, o1);
+                    store_out(out + (size_t)tok * ldo + (size_t)gh * D + p + half, o2);
+                } else if (ep.rope_write_kv) {
+                    const bool is_v = gh >= ep.rope_nq + ep.rope_nkv;
+                    const int hk = gh - ep.rope_nq - (is_v ? ep.rope_nkv : 0);
+                    const int page = ep.rope_block_table[(size_t)req * ep.rope_table_stride + pos / ep.rope_page_size];
+                    __nv_bfloat16* dst = (is_v ? ep.rope_v_cache : ep.rope_k_cache) +
+                        (((size_t)page * ep.rope_nkv + hk) * ep.rope_page_size + pos % ep.rope_page_size) * D;
+                    dst[p] = __float2bfloat16_rn(o1);
+                    dst[p + half] = __float2bfloat16_rn(o2);
+                }
+            }
+        } else if (!gated) {
             const int slice = BM / splits;             // features this block reduces
             const int i0 = split * slice;
             for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
@@ -386,6 +457,13 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
     if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || !ep.sink_partials))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink needs %d features to be a multiple of %d, and all its tensors", N_feat, BM);
     if (ep.row_partials && ep.n_partials < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: n_partials=%d", ep.n_partials);
+    if (ep.rope_positions) {
+        const int D = ep.rope_head_dim;
+        if (bn > 64 || gated || ep.sink_resid || out_f32 || (D != 32 && D != 64 && D != 128) || ep.rope_pairs > D / 2 ||
+            N_feat != (ep.rope_nq + 2 * ep.rope_nkv) * D || N_feat % BM || !ep.rope_token_req || !ep.rope_inv_freq ||
+            (ep.rope_write_kv && (!ep.rope_block_table || !ep.rope_k_cache || !ep.rope_v_cache || ep.rope_page_size < 1)))
+            NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc_rope: at most 64 tokens, head_dim 32, 64 or 128 (not %d), %d features in whole tiles of %d, bf16 output", D, N_feat, BM);
+    }
     if ((M_tok + bn - 1) / bn > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: too many token tiles");
     CUtensorMap mw, mx;
     int rc = ns_make_map_bf16(&mw, w, N_feat, K, ldw, BM, "ns_gemm_bf16_tc");
@@ -443,4 +521,36 @@ NS_API int ns_gemm_bf16_tc_norm(const void* x, const void* w, void* out, int M_t
     ep.sink_partials = sink_partials;
     ep.sink_ld = sink_ld;
     return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, out_f32, splits, ep, error_flag, stream);
+}
+
+// The packed q/k/v projection of an attention layer with the rotation and the cache write in its epilogue (64
+// tokens at most; head_dim 32, 64 or 128; (nq + 2 nkv) * head_dim features in whole tiles of 128).  out [M_tok, ldo]
+// receives the rotated q at columns 0 .. nq * head_dim (its k and v columns are not written); k (rotated) and v go to
+// cache[page, kv head, offset, :] with page = block_table[token_req[n], positions[n] / page_size] when write_kv is
+// set.  row_partials as in ns_gemm_bf16_tc_norm (or null).
+NS_API int ns_gemm_bf16_tc_rope(const void* x, const void* w, void* out, int M_tok, int N_feat, int K, int ldx, int ldw,
+                                int ldo, int splits, const float* row_partials, int n_partials, int hidden, float eps,
+                                const int* positions, const int* token_req, const int* block_table, int table_stride,
+                                const float* inv_freq, void* k_cache, void* v_cache, int page_size, int nq, int nkv,
+                                int head_dim, int rot_pairs, int write_kv, int* error_flag, cudaStream_t stream) {
+    GemmEpilogue ep = {};
+    ep.row_partials = row_partials;
+    ep.n_partials = n_partials;
+    ep.inv_hidden = hidden > 0 ? 1.f / (float)hidden : 0.f;
+    ep.eps = eps;
+    ep.rope_positions = positions;
+    ep.rope_token_req = token_req;
+    ep.rope_block_table = block_table;
+    ep.rope_table_stride = table_stride;
+    ep.rope_inv_freq = inv_freq;
+    ep.rope_k_cache = (__nv_bfloat16*)k_cache;
+    ep.rope_v_cache = (__nv_bfloat16*)v_cache;
+    ep.rope_page_size = page_size;
+    ep.rope_nq = nq;
+    ep.rope_nkv = nkv;
+    ep.rope_head_dim = head_dim;
+    ep.rope_pairs = rot_pairs;
+    ep.rope_write_kv = write_kv;
+    if (!positions) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc_rope: no positions");
+    return gemm_tc_host(x, w, out, M_tok, N_feat, K, ldx, ldw, ldo, 0, splits, ep, error_flag, stream);
 }

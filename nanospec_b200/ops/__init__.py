@@ -141,9 +141,12 @@ def check_kernel_errors(device: torch.device | None = None) -> None:
         code = int(st.error.item())
         if code:
             st.error.zero_()
-            what = {1: "the TMA producer waited for a free stage", 2: "the MMA issuer waited for a tile",
-                    3: "the epilogue waited for the accumulator", 4: "copies in flight did not land"}.get(code, "?")
-            raise KernelError(f"tcgen05 matrix product gave up after two seconds: {what} (code {code}); its output is not valid")
+            what = {1: "matrix product: the TMA producer waited for a free stage", 2: "matrix product: the MMA issuer waited for a tile",
+                    3: "matrix product: the epilogue waited for the accumulator", 4: "matrix product: copies in flight did not land",
+                    11: "prefill attention: the loader waited for a free stage", 12: "prefill attention: the MMA issuer waited",
+                    13: "prefill attention: a softmax warp waited", 21: "decode attention: the loader waited for a free stage",
+                    22: "decode attention: a warp waited for its keys"}.get(code, "?")
+            raise KernelError(f"a kernel gave up after waiting two seconds on an mbarrier - {what} (code {code}); its output is not valid")
 
 
 def gemm_splits(M: int, N: int, K: int) -> int:
@@ -316,6 +319,38 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_req: torch.T
     lib.call("ns_rope_kv_write", qkv.data_ptr(), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), inv_freq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_size, nq, nkv,
              head_dim, inv_freq.numel(), n, int(bool(write_kv)), dtype_code(qkv.dtype), _stream())
+
+
+FUSE_ROPE = True  # short steps rotate q and k and write k and v to the cache in the projection's epilogue
+
+
+def linear_rope(x, w: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                inv_freq: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, nq: int, nkv: int,
+                head_dim: int, write_kv: bool = True) -> bool:
+    """The packed [q | k | v] projection with the rotation and the cache write in its epilogue
+    (csrc/gemm_tcgen05.cu): out[:, : nq * head_dim] receives the rotated q; k (rotated) and v go to the cache.
+    `x` may be a `RowScaled`.  Returns False, having done nothing, when the step or the sizes do not fit
+    (more than 64 tokens, a head size other than 32, 64 or 128, features that do not fill tiles of 128, ...)."""
+    xt = x.x if isinstance(x, RowScaled) else x
+    M, K = xt.shape
+    N = w.shape[0]
+    if not (FUSE_ROPE and USE_TENSOR_CORE_GEMM and xt.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and 0 < M <= 64
+            and (TENSOR_CORE_GEMM_MAX_TOKENS is None or M <= TENSOR_CORE_GEMM_MAX_TOKENS)
+            and head_dim in (32, 64, 128) and N == (nq + 2 * nkv) * head_dim and N % 128 == 0 and w.shape[1] == K
+            and _tma_ok(xt, w) and out.shape == (M, N) and out.stride(1) == 1 and k_cache.dtype == torch.bfloat16
+            and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.dtype == torch.int32
+            and block_table.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()):
+        return False
+    _cuda(xt, w, out, positions, token_req, block_table, inv_freq, k_cache, v_cache)
+    _i32(positions, "positions"), _i32(token_req, "token_req")
+    scaled = x if isinstance(x, RowScaled) else None
+    lib.call("ns_gemm_bf16_tc_rope", xt.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, xt.stride(0), w.stride(0),
+             out.stride(0), gemm_splits(M, N, K), _ptr(scaled.partials if scaled is not None else None),
+             scaled.partials.shape[1] if scaled is not None else 0, scaled.hidden if scaled is not None else 0,
+             float(scaled.eps) if scaled is not None else 0.0, positions.data_ptr(), token_req.data_ptr(),
+             block_table.data_ptr(), block_table.stride(0), inv_freq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+             int(page_size), nq, nkv, head_dim, inv_freq.numel(), int(bool(write_kv)), _tc(xt.device).error.data_ptr(), _stream())
+    return True
 
 
 GATE_BLOCK = 64  # gate and up rows alternate in runs of this many in a packed projection that the fused kernel takes

@@ -34,6 +34,8 @@ _SIGNATURES: dict[str, list] = {
     "ns_attention_decode_tma": [_P, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "ns_gemm_bf16_tc_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _P, _P],
     "ns_rope_token_kernel_from": [_I],
+    "ns_gemm_bf16_tc_rope": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                             _P, _P],
     "ns_set_pdl": [_I],
     "ns_attention_decode_stages": [_I],
     "ns_gemm_bf16_tc": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],

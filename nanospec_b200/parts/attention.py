@@ -72,11 +72,14 @@ class GQAAttention(Part):
         return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_o)
 
     def forward(self, x, ctx: StepContext, lane: LaneView, writes: bool = True, sink: ops.NormSink | None = None):
-        qkv = ops.linear(x, self.w_qkv, ctx.buffer("qkv", self.q_size + 2 * self.kv_size))
-        if self.position is not None:
-            self.position.rotate_and_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes)
-        elif writes:
-            ops.kv_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim)
+        qkv = ctx.buffer("qkv", self.q_size + 2 * self.kv_size)
+        fused = getattr(self.position, "project_rotate_store", None)
+        if fused is None or not fused(x, self.w_qkv, qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes):
+            ops.linear(x, self.w_qkv, qkv)
+            if self.position is not None:
+                self.position.rotate_and_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes)
+            elif writes:
+                ops.kv_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn_out", self.q_size)
         ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window)
         return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)

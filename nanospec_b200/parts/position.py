@@ -9,6 +9,9 @@ Interface of a position part used by an attention mixer:
     rotate_and_store(qkv, ctx, lane, nq, nkv, head_dim, writes)
         rotates q and k inside the packed projection [q | k | v]; when `writes`, stores the
         rotated k and v at each token's slot of `lane`.
+    project_rotate_store(x, w_qkv, qkv, ctx, lane, nq, nkv, head_dim, writes) -> bool      (optional)
+        the projection itself with the rotation and the store in its epilogue; False (nothing done)
+        when the step does not fit, and the mixer then runs the projection and `rotate_and_store`.
 """
 
 from __future__ import annotations
@@ -63,3 +66,8 @@ class RotaryEncoding(Part):
                          head_dim: int, writes: bool) -> None:
         ops.rope_kv_write(qkv, ctx.positions, ctx.token_req, lane.block_table, self.inv_freq, lane.k, lane.v,
                           lane.page_size, nq, nkv, head_dim, write_kv=writes)
+
+    def project_rotate_store(self, x, w_qkv: torch.Tensor, qkv: torch.Tensor, ctx: StepContext, lane: LaneView, nq: int,
+                             nkv: int, head_dim: int, writes: bool) -> bool:
+        return ops.linear_rope(x, w_qkv, qkv, ctx.positions, ctx.token_req, lane.block_table, self.inv_freq, lane.k, lane.v,
+                               lane.page_size, nq, nkv, head_dim, write_kv=writes)

@@ -145,6 +145,63 @@ def test_norm_epilogues(M, H, K, N2):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("M,nq,nkv,d,K,page", [(1, 4, 2, 64, 256, 8), (8, 32, 8, 128, 4096, 16), (20, 8, 4, 32, 520, 4), (33, 2, 1, 128, 128, 16)])
+def test_rope_epilogue(M, nq, nkv, d, K, page):
+    """The packed projection with rotation and cache write in its epilogue against the projection followed by
+    the rotation kernel: the same q, the same pages (a padding row among the tokens is skipped)."""
+    o = ops()
+    g = torch.Generator().manual_seed(M + d)
+    N = (nq + 2 * nkv) * d
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))).to(DEV)
+    n_pages = M * 3 + 4
+    positions = torch.randint(0, 3 * page, (M,), generator=g).to(torch.int32)
+    token_req = torch.arange(M, dtype=torch.int32)
+    if M > 4:
+        token_req[3] = -1
+    tables = torch.randperm(n_pages, generator=g)[: M * 3].to(torch.int32).view(M, 3).to(DEV)
+    positions, token_req = positions.to(DEV), token_req.to(DEV)
+    caches = []
+    outs = []
+    keep = o.TENSOR_CORE_GEMM_MAX_TOKENS
+    o.TENSOR_CORE_GEMM_MAX_TOKENS = 64  # the kernel's own limit, whatever the engine's choice of library is
+    try:
+        for fused in (True, False):
+            kc = torch.zeros(n_pages, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+            vc = torch.zeros_like(kc)
+            out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+            if fused:
+                assert o.linear_rope(x, w, out, positions, token_req, tables, inv_freq, kc, vc, page, nq, nkv, d)
+            else:
+                o.linear(x, w, out)
+                o.rope_kv_write(out, positions, token_req, tables, inv_freq, kc, vc, page, nq, nkv, d)
+            torch.cuda.synchronize()
+            o.check_kernel_errors()
+            outs.append(out[:, : nq * d].float())
+            caches.append((kc.float(), vc.float()))
+    finally:
+        o.TENSOR_CORE_GEMM_MAX_TOKENS = keep
+    live = (token_req >= 0)
+    # the fused epilogue rotates the fp32 sums; the two-kernel path rounds them to bf16 first
+    torch.testing.assert_close(outs[0][live], outs[1][live], rtol=2 ** -6, atol=2e-2)
+    torch.testing.assert_close(caches[0][0], caches[1][0], rtol=2 ** -6, atol=2e-2)
+    torch.testing.assert_close(caches[0][1], caches[1][1], rtol=2 ** -6, atol=2e-2)
+    assert float(caches[0][0].abs().sum()) > 0
+    # and against float64 for the keys: rotate the exact products
+    full = x.double() @ w.double().T
+    k = full[:, nq * d: (nq + nkv) * d].view(M, nkv, d)
+    ang = positions.double()[:, None] * inv_freq.double()[None, :]
+    c, s_ = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    k_rot = torch.cat([k[..., : d // 2] * c - k[..., d // 2:] * s_, k[..., d // 2:] * c + k[..., : d // 2] * s_], dim=-1)
+    for n in range(M):
+        if int(token_req[n]) < 0:
+            continue
+        pg = int(tables[n, int(positions[n]) // page])
+        got = caches[0][0][pg, :, int(positions[n]) % page, :]
+        torch.testing.assert_close(got.double(), k_rot[n], rtol=2 ** -7, atol=1e-2)
+
+
 def test_strided_rows_and_output():
     x, w, want = case(24, 192, 128, 5, ldx=136, ldw=256)
     wide = torch.zeros(24, 400, dtype=torch.bfloat16, device=DEV)

@@ -82,7 +82,8 @@ def test_position_part_alone_matches_the_reference_frequencies():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,d,hidden,window", [(6, 3, 16, 80, 0), (4, 1, 32, 96, 0), (4, 2, 16, 64, 11)])
+@pytest.mark.parametrize("heads,kv_heads,d,hidden,window", [(6, 3, 16, 80, 0), (4, 1, 32, 96, 0), (4, 2, 16, 64, 11),
+                                                            (4, 2, 64, 128, 0), (8, 4, 32, 256, 9)])  # the last two: rotation in the projection's epilogue
 def test_attention_mixer_alone_over_two_steps(dtype, heads, kv_heads, d, hidden, window):
     """The mixer on its own cache lane: a portion, then the rest, against whole-sequence attention."""
     from nanospec_b200.config import PartSpec
