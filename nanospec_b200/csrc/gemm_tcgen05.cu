@@ -94,6 +94,11 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 
 __device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
 __device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+// two neighbouring outputs at an address aligned for the pair
+__device__ __forceinline__ void store_out2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_out2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
 
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
@@ -208,13 +213,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;  // the TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;
         if (kNorm) {
-            // while the products run: each token's scale, one warp per token, partial sums in ascending order
+            // While the products run: each token's scale.  A warp takes a token at a time, a lane every 32nd
+            // partial sum (all of a lane's loads are requested before the first is used), then the lanes'
+            // sums are added in a fixed tree: the same value in every block, whatever the timing.
             for (int t = warp - 2; t < BN; t += 4) {
                 float inv = 1.f;
                 if (ep.row_partials && tok0 + t < M_tok) {
                     const float* p = ep.row_partials + (size_t)(tok0 + t) * ep.n_partials;
                     float acc = 0.f;
-                    for (int i = lane; i < ep.n_partials; i += 32) acc += p[i];
+                    for (int i0 = 0; i0 < ep.n_partials; i0 += 256) {
+                        float v[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const int i = i0 + lane + 32 * k;
+                            v[k] = i < ep.n_partials ? __ldg(p + i) : 0.f;
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc += v[k];
+                    }
                     inv = rsqrtf(ns_warp_sum(acc) * ep.inv_hidden + ep.eps);
                 }
                 if (lane == 0) inv_s[t] = inv;
@@ -288,8 +304,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // per token, both members of each.  The four epilogue warps do it (they hold the first angles).
             const int D = ep.rope_head_dim, half = D / 2;
             const int npid = (BM / 2) / splits;
+            const int pid_shift = 31 - __clz(npid);                      // npid is a power of two
             for (int e = (int)threadIdx.x - 64; e >= 0 && e < tok_n * npid; e += 128) {
-                const int j = e / npid, pid = split * npid + (e - j * npid);
+                const int j = e >> pid_shift, pid = split * npid + (e & (npid - 1));
                 const int head_local = pid / half, p = pid - head_local * half;
                 const int lo = head_local * D + p, hi = lo + half;       // features within the tile
                 const int tok = tok0 + j;
@@ -329,10 +346,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
         } else if (!gated) {
-            const int slice = BM / splits;             // features this block reduces
+            const int slice = BM / splits;             // features this block reduces: a power of two
             const int i0 = split * slice;
+            const int slice_shift = 31 - __clz(slice);
             for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
-                const int j = e / slice, i = i0 + (e - j * slice);
+                const int j = e >> slice_shift, i = i0 + (e & (slice - 1));
                 if (n0 + i >= N_feat) continue;
                 float v[kMaxSplits];
 #pragma unroll
@@ -363,23 +381,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else {
             // features 0..63 of the tile are gates, 64..127 the matching ups: this block finishes
             // 64 / splits outputs per token
-            const int slice = (BM / 2) / splits;
+            const int slice = (BM / 2) / splits;        // a power of two, 8 at least
             const int i0 = split * slice;
             const int o0 = n0 / 2;                      // first output feature of the tile
-            for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
-                const int j = e / slice, i = i0 + (e - j * slice);
+            const int half_shift = 31 - __clz(slice) - 1;
+            // two neighbouring outputs per thread and turn: 8-byte reads of the partial tiles, one 4-byte store
+            for (int e = threadIdx.x; e < tok_n * (slice / 2); e += kThreads) {
+                const int j = e >> half_shift, i = i0 + 2 * (e & (slice / 2 - 1));
                 if (2 * (o0 + i) >= N_feat) continue;
-                float g[kMaxSplits], u[kMaxSplits];
+                float2 gs = make_float2(0.f, 0.f), us = make_float2(0.f, 0.f);
+                if (splits == 1) {
+                    gs = *reinterpret_cast<const float2*>(stage_f32 + j * BM + i);
+                    us = *reinterpret_cast<const float2*>(stage_f32 + j * BM + BM / 2 + i);
+                } else {
+                    float2 g[kMaxSplits], u[kMaxSplits];
 #pragma unroll
-                for (int s = 0; s < kMaxSplits; ++s) {
-                    g[s] = s < splits ? partial(j * BM + i, s) : 0.f;
-                    u[s] = s < splits ? partial(j * BM + BM / 2 + i, s) : 0.f;
+                    for (int s = 0; s < kMaxSplits; ++s) {
+                        g[s] = s < splits ? make_float2(partial(j * BM + i, s), partial(j * BM + i + 1, s)) : make_float2(0.f, 0.f);
+                        u[s] = s < splits ? make_float2(partial(j * BM + BM / 2 + i, s), partial(j * BM + BM / 2 + i + 1, s))
+                                          : make_float2(0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int s = 0; s < kMaxSplits; ++s) {
+                        gs.x += g[s].x; gs.y += g[s].y;
+                        us.x += u[s].x; us.y += u[s].y;
+                    }
                 }
-                float gs = 0.f, us = 0.f;
-#pragma unroll
-                for (int s = 0; s < kMaxSplits; ++s) { gs += g[s]; us += u[s]; }
-                if (kNorm) { gs *= inv_s[j]; us *= inv_s[j]; }
-                store_out(out + (size_t)(tok0 + j) * ldo + o0 + i, (gs / (1.f + expf(-gs))) * us);
+                if (kNorm) {
+                    const float inv = inv_s[j];
+                    gs.x *= inv; gs.y *= inv; us.x *= inv; us.y *= inv;
+                }
+                // silu(gate) * up; the hardware exponential and division (about 2 ulp in float) are far below the
+                // rounding of the result
+                const float r0 = __fdividef(gs.x, 1.f + __expf(-gs.x)) * us.x;
+                const float r1 = __fdividef(gs.y, 1.f + __expf(-gs.y)) * us.y;
+                OutT* dst = out + (size_t)(tok0 + j) * ldo + o0 + i;
+                if (2 * (o0 + i + 1) < N_feat && (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(OutT))) == 0) {
+                    store_out2(dst, r0, r1);
+                } else {
+                    store_out(dst, r0);
+                    if (2 * (o0 + i + 1) < N_feat) store_out(dst + 1, r1);
+                }
             }
         }
     }
