@@ -11,12 +11,14 @@
 //                    maximum has grown by more than a factor 256
 //   O += P V         tcgen05.mma, P read from TMEM (so the tensor core's shared-memory reads are V
 //                    alone), V as it lies in the cache (dim contiguous: an MN-major operand)
-// Warp roles: warp 0 (one lane) issues the TMA loads - the keys of a block come from 64/page_size
-// cache pages, found through the request's block table; warp 1 (one lane) issues the MMAs and
-// owns the TMEM allocation; warps 2-5 and 6-9 are the softmax threads of the two tiles and write the output.  S is double
-// buffered in TMEM, so the scores of block j+1 are computed while block j is in the softmax.  The
-// scores of block j+2 go where P of block j lies: the MMAs of one thread run in the order they were
-// issued, and that thread issues them after the product that reads P of block j.
+// Warp roles: warp 0 (one elected lane) issues the TMA loads - the keys of a block come from 64/page_size
+// cache pages, found through the request's block table; warp 1 issues the MMAs of S = Q K^T and owns the
+// TMEM allocation; warp 2 issues the MMAs of O += P V; warps 3-6 and 7-10 are the softmax threads of the
+// two tiles and write the output.  S is double buffered in TMEM, so the scores of blocks j+1 and j+2 are
+// computed while block j is in the softmax; the scores of block j+2 go where P of block j lies, once the
+// product that read it has completed (an mbarrier that the P V issuer commits to).  The two products have
+// a warp each because issuing a tcgen05.mma blocks until the tensor core takes it: one warp that also
+// waited for the softmax left the tensor core idle during its waits.
 //
 // Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
 // block winds down.  Head sizes other than 128, page sizes other than 8/16/32/64 and windows
@@ -30,7 +32,7 @@ constexpr int kTiles = 2;      // query tiles per block: they share every key/va
 constexpr int kBK = 64;        // keys per block
 constexpr int kD = 128;        // head size
 constexpr int kKvStages = 4;     // key/value blocks in flight: later blocks are loaded while block j is in the softmax
-constexpr int kTcThreads = 64 + kTiles * 128;
+constexpr int kTcThreads = 96 + kTiles * 128;
 constexpr float kLog2eTc = 1.4426950408889634f;
 
 constexpr int kQBytes = kBQ * kD * 2;          // 32 KB per tile: two halves of 128 rows x 128 B
@@ -64,15 +66,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t q_smem = base;                                   // [tile]
     const uint32_t kv_smem = q_smem + kTiles * kQBytes;             // [stage][K | V]
     const uint32_t bar0 = kv_smem + kKvStages * 2 * kKBytes;
-    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], p_ready[2], o_done
+    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], s_free[2], p_ready[2], o_done
     const uint32_t q_full = bar0;
     auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
-    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 5 + which); };
+    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 7 + which); };
     auto s_full = [&](int t, int b) { return tile_bar(t, b); };
-    auto p_ready = [&](int t, int b) { return tile_bar(t, 2 + b); };
-    auto o_done = [&](int t) { return tile_bar(t, 4); };
-    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 5);
+    auto s_free = [&](int t, int b) { return tile_bar(t, 2 + b); };
+    auto p_ready = [&](int t, int b) { return tile_bar(t, 4 + b); };
+    auto o_done = [&](int t) { return tile_bar(t, 6); };
+    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 7);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads vary fastest: the host lists the tiles with the most keys first, and blocks are
@@ -90,6 +93,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int t = 0; t < kTiles; ++t) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(s_full(t, b), 1);
+                mbar_init(s_free(t, b), 1);
                 mbar_init(p_ready(t, b), 128);
             }
             mbar_init(o_done(t), 1);
@@ -150,19 +154,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: the warp runs the loop, one elected lane issues ----------------
+        // ---------------- issuer of S = Q K^T: the warp runs the loop, one elected lane issues ----------------
+        // tcgen05.mma issue blocks until the tensor core has taken the instruction, so a warp that also
+        // waited for the softmax would leave the tensor core idle meanwhile: the two products have a warp each.
         constexpr uint32_t idesc_s = idesc_tc(kBK, false);
-        constexpr uint32_t idesc_o = idesc_tc(kD, true);
         bool ok = mbar_wait_warp(q_full, 0);
-        // scores of key block j for every tile that sees it
-        auto issue_scores = [&](int j) -> bool {
+        for (int j = 0; ok && j < n_blocks; ++j) {
             const int s = j % kKvStages, b = j & 1;
-            if (!mbar_wait_warp(kv_full(s), (uint32_t)(j / kKvStages) & 1u)) return false;
+            // Three things must hold before the scores of block j are issued: its keys have landed, and for each
+            // tile S[t][b] is free (it held P of block j-2, and the product that read it is done).  One lane each
+            // polls one of the barriers, so the warp pays one wait, not three.
+            {
+                // the same instructions for the three lanes, with a barrier each
+                const int tile = lane == 1 ? 0 : 1;
+                const bool frees = lane >= 1 && lane <= kTiles && j >= 2 && j < (tile == 0 ? nblk_t[0] : nblk_t[1]);
+                const uint32_t bar = lane == 0 ? kv_full(s) : s_free(tile, b);
+                const uint32_t par = lane == 0 ? ((uint32_t)(j / kKvStages) & 1u) : (((uint32_t)(j >> 1) & 1u) ^ 1u);
+                bool mine = true;
+                if (lane == 0 || frees) mine = mbar_wait(bar, par);
+                if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+            }
             tc_fence_after();
             const uint32_t k_src = kv_smem + s * 2 * kKBytes;
             for (int t = 0; t < kTiles; ++t) {
                 if (j >= nblk_t[t]) continue;
-                // S[t][b] held P of block j-2; the product that read it was issued before this
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t qa = q_smem + t * kQBytes + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
@@ -171,12 +186,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 if (elect_one()) umma_commit(s_full(t, b));
             }
-            return true;
-        };
-        if (ok && n_blocks > 0) ok = issue_scores(0);
+        }
+        if (!ok && lane == 0) atomicExch(error_flag, kErrAttnMma);
+    } else if (warp == 2) {
+        // ---------------- issuer of O += P V ----------------
+        constexpr uint32_t idesc_o = idesc_tc(kD, true);
+        bool ok = true;
         for (int j = 0; ok && j < n_blocks; ++j) {
-            if (j + 1 < n_blocks) ok = issue_scores(j + 1);  // the next block's scores run under this block's softmax
-            if (!ok) break;
             const int s = j % kKvStages, b = j & 1;
             const uint32_t v_src = kv_smem + s * 2 * kKBytes + kKBytes;
             for (int t = 0; t < kTiles && ok; ++t) {
@@ -188,14 +204,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (elect_one())
                         umma_bf16_ts(tmem_o(t), tmem_s(t, b) + kk * 8, smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
                                      idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                if (elect_one()) umma_commit(o_done(t));    // this tile's accumulator holds blocks 0..j
+                if (elect_one()) {
+                    umma_commit(o_done(t));      // this tile's accumulator holds blocks 0..j
+                    umma_commit(s_free(t, b));   // and S[t][b] may take the scores of block j+2
+                }
             }
-            if (elect_one()) umma_commit(kv_empty(s));      // the stage's keys and values have been read by every tile
+            // The stage's values have been read by every tile; its keys were read by the scores of block j,
+            // which were complete before the softmax that made P could start.
+            if (ok && elect_one()) umma_commit(kv_empty(s));
         }
         if (!ok && lane == 0) atomicExch(error_flag, kErrAttnMma);
-    } else if (warp >= 2) {
+    } else if (warp >= 3) {
         // ---------------- softmax and output: one query row per thread, one warpgroup per tile ----------------
-        const int t = (warp - 2) >> 2;                             // the tile this warpgroup serves
+        const int t = (warp - 3) >> 2;                             // the tile this warpgroup serves
         const int quarter = warp & 3;                              // the TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;                       // TMEM lane = query row of the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
