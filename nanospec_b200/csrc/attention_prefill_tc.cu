@@ -228,8 +228,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool ok = true;
         for (int j = 0; j < my_blocks; ++j) {
             const int b = j & 1;
-            if (lane == 0) ok = mbar_wait(s_full(t, b), (uint32_t)(j >> 1) & 1u);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            ok = mbar_wait_warp(s_full(t, b), (uint32_t)(j >> 1) & 1u);
             if (!ok) break;
             tc_fence_after();
             uint32_t sv[2][32];
@@ -277,8 +276,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 // Some row's reference point moved: this warp's rows of the accumulator are rescaled.  They
                 // must hold block j-1 first; block j is not added before this warp has arrived below, so
                 // the barrier cannot be a phase further.
-                if (lane == 0) ok = mbar_wait(o_done(t), (uint32_t)(j - 1) & 1u);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = mbar_wait_warp(o_done(t), (uint32_t)(j - 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll 1
@@ -297,8 +295,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_arrive(p_ready(t, b));
         }
         if (ok && my_blocks > 0) {
-            if (lane == 0) ok = mbar_wait(o_done(t), (uint32_t)(my_blocks - 1) & 1u);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            ok = mbar_wait_warp(o_done(t), (uint32_t)(my_blocks - 1) & 1u);
         }
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, kErrAttnSoftmax);
