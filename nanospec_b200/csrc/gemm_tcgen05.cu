@@ -248,9 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (p < ep.rope_pairs) sincosf((float)ep.rope_positions[tok0 + j] * ep.rope_inv_freq[p], &rope_sin0, &rope_cos0);
             }
         }
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(accum_bar, 0);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const bool ok = mbar_wait_warp(accum_bar, 0);
         if (!ok) {
             if (lane == 0) { failed = 1; atomicExch(error_flag, kErrEpilogueWait); }
         } else {
