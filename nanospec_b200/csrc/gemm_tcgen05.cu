@@ -154,59 +154,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint32_t tmem_base;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
 
-    if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer ----------------
+    if (warp == 0) {
+        // ---------------- TMA producer: the warp runs the loop converged, one elected lane issues ----------------
         // The weights do not depend on the previous kernel: their first tiles are requested before
         // this kernel waits for it, so they stream in while the predecessor is still running.  The
         // token tiles of those stages follow after the wait (each stage's barrier counts both).
         int issued = 0;
         bool ok = true;
         const int early = min(kb_count, C::kStages);
-        for (int i = 0; i < early; ++i) {
-            mbar_expect_tx(full_bar(i), C::kStageBytes);
-            tma_load_2d(base + i * C::kStageBytes, &map_w, (kb_begin + i) * BK, n0, full_bar(i));
+        if (elect_one()) {
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(full_bar(i), C::kStageBytes);
+                tma_load_2d(base + i * C::kStageBytes, &map_w, (kb_begin + i) * BK, n0, full_bar(i));
+            }
         }
         ns_pdl_wait();
-        for (int i = 0; i < early; ++i) {
-            tma_load_2d(base + i * C::kStageBytes + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(i));
-            ++issued;
+        if (elect_one()) {
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(base + i * C::kStageBytes + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(i));
         }
+        issued = early;
         for (int i = early; i < kb_count; ++i) {
             const int s = i % C::kStages;
             const uint32_t ph = (uint32_t)(i / C::kStages) & 1u;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; atomicExch(error_flag, kErrProducerWait); break; }
-            mbar_expect_tx(full_bar(s), C::kStageBytes);
-            const uint32_t a = base + s * C::kStageBytes;
-            tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, full_bar(s));
-            tma_load_2d(a + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(s));
+            if (!mbar_wait_warp(empty_bar(s), ph ^ 1u)) {
+                ok = false;
+                if (lane == 0) atomicExch(error_flag, kErrProducerWait);
+                break;
+            }
+            if (elect_one()) {
+                mbar_expect_tx(full_bar(s), C::kStageBytes);
+                const uint32_t a = base + s * C::kStageBytes;
+                tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, full_bar(s));
+                tma_load_2d(a + C::kABytes, &map_x, (kb_begin + i) * BK, tok0, full_bar(s));
+            }
             ++issued;
         }
         if (!ok) {
             // wait, bounded, for the copies that are still in flight before the block may exit
-            failed = 1;
+            if (lane == 0) failed = 1;
             for (int i = max(0, issued - C::kStages); i < issued; ++i)
-                if (!mbar_wait(full_bar(i % C::kStages), (uint32_t)(i / C::kStages) & 1u)) {
-                    atomicExch(error_flag, kErrDrainWait);
+                if (!mbar_wait_warp(full_bar(i % C::kStages), (uint32_t)(i / C::kStages) & 1u)) {
+                    if (lane == 0) atomicExch(error_flag, kErrDrainWait);
                     break;
                 }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the warp runs the loop converged, one elected lane issues ----------------
         constexpr uint32_t idesc = instr_desc<BN>();
         for (int i = 0; i < kb_count; ++i) {
             const int s = i % C::kStages;
             const uint32_t ph = (uint32_t)(i / C::kStages) & 1u;
-            if (!mbar_wait(full_bar(s), ph)) { failed = 1; atomicExch(error_flag, kErrMmaWait); break; }
+            if (!mbar_wait_warp(full_bar(s), ph)) {
+                if (lane == 0) { failed = 1; atomicExch(error_flag, kErrMmaWait); }
+                break;
+            }
             tc_fence_after();
             const uint32_t a = base + s * C::kStageBytes;
             const uint32_t b = a + C::kABytes;
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-                umma_bf16(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
-                          (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+            }
         }
-        umma_commit(accum_bar);         // the accumulator is complete once every MMA above has finished
+        if (elect_one()) umma_commit(accum_bar);  // the accumulator is complete once every MMA above has finished
     } else if (warp >= 2) {
         // ---------------- epilogue ----------------
         ns_pdl_wait();           // before anything is written that the previous kernel may still read
