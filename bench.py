@@ -240,6 +240,9 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        # the one number the reference publishes for this architecture: 137 tok/s at batch 1 on an H100
+        # (its README.md:76); the headline metric here (batch 8) has no published counterpart
+        "vs_published_b1_h100": round(points["decode_b1"] / 137.0, 2),
         "clocks": clock_rec,
     }
 
