@@ -139,17 +139,19 @@ def cmd_profile(args) -> int:
         "8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
                    num_key_value_heads=8, head_dim=128, layers=32, factor=8.0),
         "3b": dict(vocab_size=128256, hidden_size=3072, intermediate_size=8192, num_attention_heads=24,
-                   num_key_value_heads=8, head_dim=128, layers=28, factor=32.0),
+                   num_key_value_heads=8, head_dim=128, layers=28, factor=32.0, tie_word_embeddings=True),
         "1b": dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
-                   num_key_value_heads=8, head_dim=64, layers=16, factor=32.0),
+                   num_key_value_heads=8, head_dim=64, layers=16, factor=32.0, tie_word_embeddings=True),
     }
     sh = dict(shapes[args.shape])
     layers = args.layers or sh.pop("layers")
     sh.pop("layers", None)
     factor = sh.pop("factor")
-    cfg = LlamaConfig(**sh, num_hidden_layers=layers, rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
-                      rope_scaling=Llama3RopeScaling(factor, 1.0, 4.0, 8192))
+    cfg = LlamaConfig(**sh, num_hidden_layers=layers, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=max(8192, args.context + 512), rope_scaling=Llama3RopeScaling(factor, 1.0, 4.0, 8192))
     model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
+    if args.what in ("batch", "mixed"):
+        return _profile_workload(args, cfg, model)
     args.max_running = max(args.batch, 1)
     args.max_admit = 64
     pages = (args.batch + (1 if args.what == "prefill" else 0)) * (-(-(args.context + 256 + args.steps) // args.block_size) + 1) + 8
@@ -210,6 +212,57 @@ def cmd_profile(args) -> int:
     return 0
 
 
+def _profile_workload(args, cfg, model) -> int:
+    """`batch`: continuous batching of --batch requests with prompt lengths uniform in [--prompt-min, --context] and
+    --new-tokens new tokens each.  `mixed`: --long prompts of --context tokens prefilled in portions of
+    --prefill-chunk beside --batch requests that decode (temperature 1.0, fixed seeds)."""
+    import time
+
+    import torch
+
+    from .engine import SamplingParams
+
+    g = torch.Generator().manual_seed(0)
+    bs = args.block_size
+    if args.what == "batch":
+        lens = torch.randint(args.prompt_min, args.context + 1, (args.batch,), generator=g).tolist()
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+        args.max_running, args.max_admit = args.batch, 64
+        engine = _engine(model, args, sum(-(-(n + args.new_tokens) // bs) + 1 for n in lens) + 16)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = engine.generate(prompts, SamplingParams(max_tokens=args.new_tokens, ignore_eos=True))
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        new = sum(len(o) for o in outs)
+        print(json.dumps({"what": "batch", "shape": args.shape, "requests": args.batch, "prompt_tokens": sum(lens), "new_tokens": new,
+                          "seconds": round(dt, 3), "steps": engine.steps, "new_tokens_per_s": round(new / dt, 1),
+                          "all_tokens_per_s": round((sum(lens) + new) / dt, 1)}), flush=True)
+        return 0
+    dec = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist()
+           for n in torch.randint(32, 512, (args.batch,), generator=g)]
+    longs = [torch.randint(0, cfg.vocab_size, (args.context,), generator=g).tolist() for _ in range(args.long)]
+    args.max_running, args.max_admit = args.batch + args.long, 64
+    pages = sum(-(-(len(p) + 4 * args.context // args.prefill_chunk + 64) // bs) + 1 for p in dec) + args.long * (args.context // bs + 8) + 16
+    engine = _engine(model, args, pages)
+    budget = 4 * args.context // args.prefill_chunk + 32   # the decoders outlive the prompts
+    reqs = [engine.add(p, SamplingParams(max_tokens=budget, temperature=1.0, seed=7 + i, ignore_eos=True)) for i, p in enumerate(dec)]
+    while any(r.state == "waiting" or (r.state == "running" and r.pending > 1) for r in reqs):
+        engine.step()
+    lreqs = [engine.add(p, SamplingParams(max_tokens=2, temperature=1.0, seed=99 + i, ignore_eos=True)) for i, p in enumerate(longs)]
+    torch.cuda.synchronize()
+    t0, s0 = time.perf_counter(), engine.steps
+    while any(r.state != "done" for r in lreqs):
+        engine.step()
+    torch.cuda.synchronize()
+    dt, steps = time.perf_counter() - t0, engine.steps - s0
+    print(json.dumps({"what": "mixed", "shape": args.shape, "decoding_requests": args.batch, "long_prompts": args.long,
+                      "prompt_tokens_each": args.context, "portion": args.prefill_chunk, "seconds": round(dt, 3), "steps": steps,
+                      "ms_per_step": round(1000 * dt / steps, 3), "prefill_tokens_per_s": round(args.long * args.context / dt, 1),
+                      "decoded_meanwhile": steps * args.batch}), flush=True)
+    return 0
+
+
 def cmd_random_weights(args) -> int:
     from .config import Llama3RopeScaling, LlamaConfig
     from .weights import write_random_model
@@ -267,7 +320,12 @@ def main(argv: list[str] | None = None) -> int:
     pr.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (smaller captures)")
     pr.add_argument("--batch", type=int, default=8)
     pr.add_argument("--context", type=int, default=1024)
-    pr.add_argument("--what", choices=["decode", "prefill"], default="decode")
+    pr.add_argument("--what", choices=["decode", "prefill", "batch", "mixed"], default="decode",
+                    help="decode steps; the prefill of --batch prompts; batch: continuous batching of --batch requests; "
+                         "mixed: --long prompts prefilled in portions beside --batch decoding requests")
+    pr.add_argument("--prompt-min", type=int, default=16, help="batch: shortest prompt (the longest is --context)")
+    pr.add_argument("--new-tokens", type=int, default=256, help="batch: new tokens per request")
+    pr.add_argument("--long", type=int, default=8, help="mixed: number of long prompts")
     pr.add_argument("--steps", type=int, default=1, help="decode steps to time (the median is printed)")
     pr.set_defaults(fn=cmd_profile)
 
