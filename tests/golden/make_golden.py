@@ -93,4 +93,5 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # the reference's source tree: the first argument, or a folder `reference` beside this repository
+    main(sys.argv[1] if len(sys.argv) > 1 else str(Path(__file__).resolve().parents[3] / "reference"))

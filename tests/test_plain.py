@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import json
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -71,15 +72,19 @@ def test_process_by_hand():
     assert plain.plain_draw(torch.log(p), 0.9999999) == 3
 
 
-@pytest.mark.skipif(not Path("/root/reference/model/llama.py").is_file(), reason="the reference tree is not here")
+# the reference's source tree: $NANOSPEC_REFERENCE, or a folder `reference` beside this repository
+REFERENCE = Path(os.environ.get("NANOSPEC_REFERENCE", Path(__file__).resolve().parents[2] / "reference"))
+
+
+@pytest.mark.skipif(not (REFERENCE / "model" / "llama.py").is_file(), reason="the reference tree is not here")
 def test_plain_matches_the_reference_code(tiny_folders):
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, str(REFERENCE))
     try:
         from kv.allocator import BlockAllocator
         from kv.cache import AttnMeta, PagedKVCache
         from model.loader import load_model
     finally:
-        sys.path.remove("/root/reference")
+        sys.path.remove(str(REFERENCE))
     ref = load_model(tiny_folders["B"], device="cpu", dtype=torch.float32, backend="sdpa")
     cfg, w = plain.read_folder(tiny_folders["B"])
     ids = GOLDEN["B"]["prompt"]
