@@ -1,4 +1,4 @@
-// Prefill attention on the 5th-generation tensor cores (head size 128, bfloat16): portions of
+// Prefill attention on the 5th-generation tensor cores (head sizes 64 and 128, bfloat16): portions of
 // prompts, causal by absolute position, keys and values read from the paged cache.
 //
 // One block = 256 consecutive query tokens of one request (two tiles of 128, each with its own softmax
@@ -21,7 +21,7 @@
 // waited for the softmax left the tensor core idle during its waits.
 //
 // Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
-// block winds down.  Head sizes other than 128, page sizes other than 8/16/32/64 and windows
+// block winds down.  Other head sizes, page sizes other than 8/16/32/64 and windows
 // are served by the m16n8k16 kernel of attention_prefill.cu.
 #include "tcgen05_utils.cuh"
 
@@ -30,14 +30,17 @@ namespace {
 constexpr int kBQ = 128;       // query rows per tile = UMMA M
 constexpr int kTiles = 2;      // query tiles per block: they share every key/value block
 constexpr int kBK = 64;        // keys per block
-constexpr int kD = 128;        // head size
 constexpr int kKvStages = 4;     // key/value blocks in flight: later blocks are loaded while block j is in the softmax
 constexpr int kTcThreads = 96 + kTiles * 128;
 constexpr float kLog2eTc = 1.4426950408889634f;
 
-constexpr int kQBytes = kBQ * kD * 2;          // 32 KB per tile: two halves of 128 rows x 128 B
-constexpr int kKBytes = kBK * kD * 2;          // 16 KB: two halves of 64 rows x 128 B
-constexpr int kSmemTc = kTiles * kQBytes + kKvStages * 2 * kKBytes + 1024 + 256;
+// sizes for head size D (64 or 128): tiles are halves of 64 columns = 128 bytes, the swizzle's row
+template <int D>
+struct TcSizes {
+    static constexpr int kQBytes = kBQ * D * 2;   // per tile: D / 64 halves of 128 rows x 128 B
+    static constexpr int kKBytes = kBK * D * 2;   // D / 64 halves of 64 rows x 128 B
+    static constexpr int kSmem = kTiles * kQBytes + kKvStages * 2 * kKBytes + 1024 + 256;
+};
 constexpr int kTmemColsTc = 512;               // S[tile][buffer] at (tile * 2 + buffer) * 64, O[tile] at 256 + tile * 128
 
 enum TcAttnError { kErrAttnLoader = 11, kErrAttnMma = 12, kErrAttnSoftmax = 13 };
@@ -54,6 +57,7 @@ __device__ __forceinline__ constexpr uint32_t idesc_tc(int n, bool b_mn_major) {
            ((uint32_t)(kBQ >> 4) << 24);
 }
 
+template <int kD>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -61,6 +65,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
                             int page_size, float scale, int* __restrict__ error_flag) {
     ns_pdl_launch_dependents();
+    constexpr int kQBytes = TcSizes<kD>::kQBytes, kKBytes = TcSizes<kD>::kKBytes;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t q_smem = base;                                   // [tile]
@@ -130,8 +135,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (elect_one()) {
             mbar_expect_tx(q_full, kTiles * kQBytes);
             for (int t = 0; t < kTiles; ++t) {  // rows past the step's tokens are zero-filled by TMA
-                tma_load_2d(q_smem + t * kQBytes, &map_q, h * kD, tok0 + t * kBQ, q_full);
-                tma_load_2d(q_smem + t * kQBytes + kBQ * 128, &map_q, h * kD + 64, tok0 + t * kBQ, q_full);
+#pragma unroll
+                for (int hh = 0; hh < kD / 64; ++hh)
+                    tma_load_2d(q_smem + t * kQBytes + hh * (kBQ * 128), &map_q, h * kD + hh * 64, tok0 + t * kBQ, q_full);
             }
         }
         const int pages_per_block = kBK / page_size;
@@ -146,10 +152,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int row = (bt[blk] * nkv + hk) * page_size;
                 const uint32_t off = (uint32_t)(i * page_size) * 128u;
                 if (elect_one()) {
-                    tma_load_2d(k_dst + off, &map_k, 0, row, kv_full(s));
-                    tma_load_2d(k_dst + kBK * 128 + off, &map_k, 64, row, kv_full(s));
-                    tma_load_2d(v_dst + off, &map_v, 0, row, kv_full(s));
-                    tma_load_2d(v_dst + kBK * 128 + off, &map_v, 64, row, kv_full(s));
+#pragma unroll
+                    for (int hh = 0; hh < kD / 64; ++hh) {
+                        tma_load_2d(k_dst + hh * (kBK * 128) + off, &map_k, hh * 64, row, kv_full(s));
+                        tma_load_2d(v_dst + hh * (kBK * 128) + off, &map_v, hh * 64, row, kv_full(s));
+                    }
                 }
             }
         }
@@ -331,24 +338,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-}  // namespace
-
-// q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
-// lane's pages [n_pages, nkv, page_size, 128]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of
-// this step, a multiple of 256).  Head size 128 only; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
-NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
-                                   long long n_pages, const int* block_table, int table_stride, const int* positions,
-                                   const int* qo_indptr, const int* tiles, int n_tiles, void* out, int o_stride, int nq,
-                                   int nkv, int d, int page_size, float scale, int* error_flag, cudaStream_t stream) {
-    if (n_tiles <= 0) return NS_OK;
-    if (d != kD) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: head_dim=%d (128 only)", d);
-    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: page_size=%d (8, 16, 32 or 64)", page_size);
-    if (nkv < 1 || nq % nkv || n_tiles > 65535)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads, %d tiles", nq, nkv, n_tiles);
-    if (q_stride % 8 || o_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
-        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: rows must be 16-byte aligned");
-    if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: no error flag");
+template <int kD>
+int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache, long long n_pages,
+                      const int* block_table, int table_stride, const int* positions, const int* qo_indptr, const int* tiles,
+                      int n_tiles, void* out, int o_stride, int nq, int nkv, int page_size, float scale, int* error_flag,
+                      cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     int rc = ns_make_map_bf16(&mq, q, (unsigned long long)n_tokens, nq * kD, q_stride, kBQ, "ns_attention_prefill_tc");
     if (rc) return rc;
@@ -359,12 +353,38 @@ NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, co
     if (rc) return rc;
     static bool configured = false;
     if (!configured) {
-        NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc));
+        NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<kD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     TcSizes<kD>::kSmem));
         configured = true;
     }
-    NS_LAUNCH((attention_prefill_tc_kernel), dim3(nq, n_tiles), kTcThreads, kSmemTc, stream, mq, mk, mv, block_table,
-              table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale,
-              error_flag);
+    NS_LAUNCH((attention_prefill_tc_kernel<kD>), dim3(nq, n_tiles), kTcThreads, TcSizes<kD>::kSmem, stream, mq, mk, mv,
+              block_table, table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size,
+              scale, error_flag);
     NS_CHECK_LAUNCH("ns_attention_prefill_tc");
     return NS_OK;
+}
+
+}  // namespace
+
+// q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
+// lane's pages [n_pages, nkv, page_size, head_dim]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of
+// this step, a multiple of 256).  Head sizes 64 and 128; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
+NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
+                                   long long n_pages, const int* block_table, int table_stride, const int* positions,
+                                   const int* qo_indptr, const int* tiles, int n_tiles, void* out, int o_stride, int nq,
+                                   int nkv, int d, int page_size, float scale, int* error_flag, cudaStream_t stream) {
+    if (n_tiles <= 0) return NS_OK;
+    if (d != 64 && d != 128) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: head_dim=%d (64 or 128)", d);
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: page_size=%d (8, 16, 32 or 64)", page_size);
+    if (nkv < 1 || nq % nkv || n_tiles > 65535)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads, %d tiles", nq, nkv, n_tiles);
+    if (q_stride % 8 || o_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: rows must be 16-byte aligned");
+    if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: no error flag");
+    if (d == 64)
+        return launch_prefill_tc<64>(q, q_stride, n_tokens, k_cache, v_cache, n_pages, block_table, table_stride, positions,
+                                     qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, error_flag, stream);
+    return launch_prefill_tc<128>(q, q_stride, n_tokens, k_cache, v_cache, n_pages, block_table, table_stride, positions,
+                                  qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, error_flag, stream);
 }

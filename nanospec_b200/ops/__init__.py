@@ -502,9 +502,9 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
-    among its tokens of this step).  Head size 128 with pages of 8 to 64 tokens and no window runs
+    among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
-    if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim == 128 and window == 0 \
+    if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         lib.call("ns_attention_prefill_tc", qkv.data_ptr(), qkv.stride(0), qkv.shape[0], lane.k.data_ptr(),
                  lane.v.data_ptr(), lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0),

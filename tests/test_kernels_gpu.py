@@ -393,12 +393,11 @@ def test_cluster_decode_attention(nq, nkv, d, page, window):
             assert float(out[len(lens):].abs().sum()) == 0.0  # the prompt portion's rows are not touched
 
 
-@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 8), (6, 1, 32), (32, 8, 64)])
-def test_tcgen05_prefill_attention(nq, nkv, page):
-    """Head size 128 takes the tcgen05 kernel: prompts from 2 to 1,500 tokens, portions that continue a
+@pytest.mark.parametrize("nq,nkv,page,d", [(8, 2, 16, 128), (4, 4, 8, 128), (6, 1, 32, 128), (32, 8, 64, 128), (8, 2, 16, 64), (6, 3, 8, 64)])
+def test_tcgen05_prefill_attention(nq, nkv, page, d):
+    """Head sizes 64 and 128 take the tcgen05 kernel: prompts from 2 to 1,500 tokens, portions that continue a
     request, tiles that end inside a page, a far key that every query must find - against the plain
     attention and against the m16n8k16 kernel."""
-    d = 128
     requests = [(1500, 1500, 7), (129, 128, 3), (700, 2, 650), (333, 70, 2), (64, 64, 63), (257, 129, 128), (1000, 300, 640)]
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=5000 // page + 40, seed=page)
     outs = {}
