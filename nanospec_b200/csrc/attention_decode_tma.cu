@@ -28,7 +28,9 @@ namespace {
 constexpr int kKeys = 64;            // keys per tile
 constexpr int kComputeWarps = 4;
 constexpr int kDtThreads = (kComputeWarps + 1) * 32;
-constexpr int kDtStages = 3;
+// tiles of 64 keys in flight per block: 96 KB of keys and values for either head size, two blocks per SM
+template <int D>
+constexpr int dt_stages() { return D == 64 ? 6 : 3; }
 constexpr int kMaxClusterSplits = 16;
 constexpr float kLog2eDt = 1.4426950408889634f;
 
@@ -58,6 +60,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
                             int head_tiles, int* __restrict__ error_flag) {
     ns_pdl_launch_dependents();
+    constexpr int kDtStages = dt_stages<D>();
     constexpr int kTileBytes = kKeys * D * 2;      // the keys or the values of one tile
     constexpr int kStageBytes = 2 * kTileBytes;
     extern __shared__ unsigned char smem_dyn[];
@@ -334,6 +337,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                       int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                       int o_stride, const int* rows, int n_tokens, int nq, int nkv, int page_size, float scale, int window,
                       int n_splits, int* error_flag, cudaStream_t stream) {
+    constexpr int kDtStages = dt_stages<D>();
     constexpr int kSmem = kDtStages * 2 * kKeys * D * 2 + (16 * D + kMaxClusterSplits + kMaxClusterSplits * 32) * 4 + 2 * kDtStages * 8 + 1024;
     static_assert(kDtStages * 2 * kKeys * D * 2 >= (kComputeWarps * 16 * (D + 8) + 128) * 4, "the warps' partial results reuse the stages");
     static bool configured = false;
