@@ -86,9 +86,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         fence_async_smem();
     }
     __syncthreads();
-    // The step's description and every key but the newest were written before the previous kernel
-    // started (by a copy, or by earlier steps): they are read before this kernel waits for it.  Only the
-    // query and the page slot of the token's own key come from the predecessor.
+    // The step's description and every key but the newest were written before this step's kernels
+    // started: by the copy that opens every step (a stream operation, which programmatic launches never
+    // overlap - so all of the previous step is complete and visible when any kernel of this step runs), or
+    // by earlier steps.  They are read before this kernel waits for its predecessor.  Only the query and
+    // the tile that holds the token's own key (written earlier in this step) come after the wait.
 
     const int n_splits = gridDim.x, split = blockIdx.x, z = blockIdx.z;
     const int n = rows ? rows[z] : z;  // the token this cluster works for
