@@ -1,9 +1,11 @@
-// Decode attention over the paged cache in bfloat16: one query token per request, the keys of
+// Decode attention over the paged cache in bfloat16, for every head size in steps of 16 up to 128 and every
+// page size (head sizes 64 and 128 with pages of 8 to 64 tokens are served by attention_decode_tma.cu): one
+// query token per request, the keys of
 // a request split over several thread blocks (split-KV), the query heads that share a kv head
 // processed together so that every key and value is read from HBM once per group.
 //
 // Grid (split, kv head x head tile, token).  A block streams its share of the keys through
-// shared memory with cp.async (two stages of 64 keys), computes scores and the weighted sum on
+// shared memory with cp.async (two or three stages of 64 keys), computes scores and the weighted sum on
 // the tensor cores (m16n8k16, the group's heads padded to 16 rows), keeps the softmax in fp32
 // (online, base 2), and writes an unnormalised partial result with its running maximum and sum.
 // The block that finishes last for a (token, kv head) - found with an atomic counter - merges

@@ -1,4 +1,5 @@
-// Token choice from fp32 logits, one thread block per row.
+// Token choice from fp32 logits: a first kernel with 16 blocks per row reduces the row's maximum, argmax and
+// sum of exponentials; a second with one block per row finds the thresholds and draws.
 //
 // Follows the reference's pure functions (spec/sampling.py:24-42, engine/engine.py:385-402):
 //   temperature == 0 : the argmax of the raw logits (lowest index on a tie);
