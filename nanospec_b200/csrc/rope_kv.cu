@@ -66,7 +66,9 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
                            T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d,
                            int rot_pairs, int write_kv) {
     ns_pdl_launch_dependents();
-    ns_pdl_wait();
+    // The token's request, position, page and angles do not come from the previous kernel (the step's
+    // description and the block table are written before the step's first kernel): they are read and
+    // computed before this kernel waits for it; only the projection itself comes after.
     extern __shared__ float cs[];  // [rot_pairs] cos, then [rot_pairs] sin
     const int n = blockIdx.x;
     const int req = token_req[n];
@@ -79,13 +81,14 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
         cs[j] = c;
         cs[rot_pairs + j] = s;
     }
-    __syncthreads();
     T* row = qkv + (size_t)n * (nq + 2 * nkv) * d;
     size_t base = 0;
     if (write_kv) {
         const int page = block_table[(size_t)req * table_stride + pos / page_size];
         base = ((size_t)page * nkv * page_size + pos % page_size) * d;  // cache[page, 0, offset, :]
     }
+    __syncthreads();
+    ns_pdl_wait();
     const size_t head_stride = (size_t)page_size * d;                   // from one kv head to the next
     const int rot_heads = write_kv ? nq + nkv : nq;
     if (kVec) {
@@ -146,11 +149,11 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
     }
 }
 
-int g_token_kernel_from = 128;  // measured in a decode step of 32 and of 64 tokens: a block per (token, head) is ahead there
+int g_token_kernel_from = 48;  // measured in a decode step of 64 tokens: 4.80 ms with a block per token, 5.02 ms with one per (token, head)
 
 }  // namespace
 
-// Steps with at least this many tokens take the kernel with one block per token (default 128).
+// Steps with at least this many tokens take the kernel with one block per token (default 48).
 NS_API int ns_rope_token_kernel_from(int n_tokens) {
     if (n_tokens < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_rope_token_kernel_from: %d", n_tokens);
     g_token_kernel_from = n_tokens;
