@@ -51,10 +51,12 @@ def write_random_model(folder: str | Path, config, seed: int = 0, generation_con
     return folder
 
 
-def random_model(config, seed: int = 0, device="cuda", dtype: torch.dtype = torch.bfloat16):
+def random_model(config, seed: int = 0, device="cuda", dtype: torch.dtype = torch.bfloat16, return_tensors: bool = False):
     """A model with random weights drawn directly on `device` (no files): for benchmarks at
     sizes where writing the folder first would only cost time.  Same distributions as
-    `write_random_model`, but the device's generator, so not the same numbers."""
+    `write_random_model`, but the device's generator, so not the same numbers.  With
+    `return_tensors` the checkpoint-named tensors are returned beside the model, so that an
+    oracle can compute with the very weights the engine holds."""
     cfg_json = config if isinstance(config, dict) else config.to_hf()
     model, _ = build_model(cfg_json, None, dtype, device)
     dev = torch.device(device)
@@ -70,4 +72,4 @@ def random_model(config, seed: int = 0, device="cuda", dtype: torch.dtype = torc
         if spec.alias is not None:
             tensors[name] = tensors[spec.alias]
     model.bind(tensors)
-    return model
+    return (model, tensors) if return_tensors else model

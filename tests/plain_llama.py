@@ -94,8 +94,8 @@ def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: i
     kk = k.repeat_interleave(g, dim=1)
     vv = v.repeat_interleave(g, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, kk) * scale
-    qpos = torch.arange(S)[:, None]
-    kpos = torch.arange(S)[None, :]
+    qpos = torch.arange(S, device=q.device)[:, None]
+    kpos = torch.arange(S, device=q.device)[None, :]
     mask = kpos <= qpos
     if window > 0:
         mask &= kpos > qpos - window
@@ -133,9 +133,10 @@ def plain_layer(x, w, i, cfg, positions, inv_freq) -> torch.Tensor:
 def plain_forward(cfg: dict, w: dict[str, torch.Tensor], ids: list[int]) -> torch.Tensor:
     """Logits [S, vocab] at every position of one whole sequence (model/llama.py:219-232,284-286)."""
     with torch.no_grad():
-        t = torch.tensor(ids, dtype=torch.int64)
-        positions = torch.arange(len(ids))
-        inv_freq = plain_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"])
+        dev = w["model.embed_tokens.weight"].device  # the weights may lie on a GPU: the same arithmetic there
+        t = torch.tensor(ids, dtype=torch.int64, device=dev)
+        positions = torch.arange(len(ids), device=dev)
+        inv_freq = plain_inv_freq(cfg["head_dim"], cfg["theta"], cfg["scaling"]).to(dev)
         x = w["model.embed_tokens.weight"][t]
         for i in range(cfg["layers"]):
             x = plain_layer(x, w, i, cfg, positions, inv_freq)
