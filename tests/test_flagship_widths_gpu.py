@@ -117,3 +117,5 @@ def test_the_whole_benchmark_shape_in_float32_under_every_cut():
             err = np.abs(got[cut][r].astype(np.float64) - truth[r]).max()
             assert err <= 3.0 * yard, f"{cut}: request {r}: {err:.3g} from float64, plain float32 is {yard:.3g} from it"
             assert np.array_equal(got[cut][r], got["whole"][r]), f"request {r}: cut {cut} differs from the whole prompt"
+    del model, w, runner
+    torch.cuda.empty_cache()  # tests after this one start their own processes on the same GPU
