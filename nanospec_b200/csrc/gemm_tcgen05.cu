@@ -76,7 +76,6 @@ enum GemmError { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kE
 template <int BN>
 struct Cfg {
     // up to 64 tokens: stages sized so that two blocks share an SM (8 to 12 tiles in flight per SM)
-    // up to 64 tokens: stages sized so that two blocks share an SM
     static constexpr int kStages = BN == 16 ? 6 : BN == 32 ? 5 : (BN == 64 ? 4 : (BN == 128 ? 6 : 4));
     static constexpr int kMinBlocks = BN <= 64 ? 2 : 1;
     static constexpr int kABytes = BM * BK * 2;
