@@ -208,6 +208,8 @@ inline int ns_make_map_bf16(CUtensorMap* map, const void* ptr, unsigned long lon
                             int box_rows, const char* who) {
     NsEncodeTiledFn fn = ns_encode_fn();
     if (!fn) NS_FAIL(NS_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+    // the kernels address rows with signed 32-bit TMA coordinates
+    if (rows > 0x7fffffffull) NS_FAIL(NS_ERR_UNSUPPORTED, "%s: a tensor of %llu rows is beyond the 2^31 - 1 that a TMA coordinate holds", who, rows);
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
