@@ -246,17 +246,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool masked = key0 + kBK - 1 > tile_pos0;         // some row of the tile does not see the whole block
             // maximum of the raw scores first (the scale is positive, so it commutes with the maximum),
             // then each weight is one fused multiply-add and one ex2
-            float mx = -INFINITY;
             if (masked) {
 #pragma unroll
-                for (int c = 0; c < kBK; ++c) {
+                for (int c = 0; c < kBK; ++c)
                     if (key0 + c > pos_row) sv[c >> 5][c & 31] = 0xff800000u;  // -inf
-                    mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < kBK; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
             }
+            // eight independent chains: one chain of 64 dependent maxima costs 64 instruction latencies
+            float mx8[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(sv[0][c]);
+#pragma unroll
+            for (int c = 8; c < kBK; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(sv[c >> 5][c & 31]));
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             // The reference point m of the exponents follows the running maximum lazily: it moves only
             // when the maximum has grown by more than 8 (a factor 256), so the accumulator is rarely
             // rescaled; weights up to 256 are exact enough in bf16 and the sums are fp32.  Block 0
@@ -265,7 +266,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool jump = cand > m + 8.f;
             const float m_new = jump ? cand : m;
             const float corr = jump ? ex2(m - m_new) : 1.f;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             // weights as bf16 pairs over the first 32 columns of this row's scores
             uint32_t pk[32];
 #pragma unroll
@@ -273,12 +274,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int c = 2 * u;
                 const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
                 const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
-                sum += p0 + p1;
+                sum4[u & 3] += p0 + p1;
                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                 pk[u] = *reinterpret_cast<uint32_t*>(&v);
             }
             tmem_st32(tmem_s(t, b) + lane_addr, pk);
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (j > 0 && __any_sync(0xffffffffu, jump)) {
                 // Some row's reference point moved: this warp's rows of the accumulator are rescaled.  They
                 // must hold block j-1 first; block j is not added before this warp has arrived below, so
