@@ -42,10 +42,21 @@ def peaks() -> tuple[dict, str]:
         try:
             p = json.load(open(path))
             out = dict(FALLBACK_PEAKS)
-            for k in out:
-                if isinstance(p.get(k), (int, float)):
-                    out[k] = float(p[k])
-            return out, "measured"
+
+            def find(node, key):  # the key at the top level, or in a nested object
+                if isinstance(node, dict):
+                    if isinstance(node.get(key), (int, float)) and not isinstance(node.get(key), bool):
+                        return float(node[key])
+                    for v in node.values():
+                        hit = find(v, key)
+                        if hit is not None:
+                            return hit
+                return None
+
+            found = {k: find(p, k) for k in out}
+            if found["hbm_gbs"] is not None or found["bf16_tflops"] is not None:
+                out.update({k: v for k, v in found.items() if v is not None and v > 0})
+                return out, "measured"
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
