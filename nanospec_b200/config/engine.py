@@ -3,6 +3,9 @@
 `max_running`, `cuda_graphs`, `record_logits`, `profile`, `head_chunk`.  The reference
 prefills a prompt whole in its admission step; `max_step_tokens`, `prefill_chunk` and
 `admission` are this engine's own additions for portions of prompts under a token budget.
+As there (engine/engine.py:74,97-106) the decode graphs are captured when the engine is
+built, so that no request pays for a capture; `capture_at_start=False` leaves each bucket
+to its first use.
 """
 
 from __future__ import annotations
@@ -26,6 +29,7 @@ class EngineConfig:
                                          # "optimistic": admit on current need, preempt the newest when pages run out
     graph_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
     lookahead: bool = True               # launch the next decode step before the last one's tokens reach the host
+    capture_at_start: bool = True        # capture every bucket's graph when the engine is built, not at first use
 
     def __post_init__(self) -> None:
         if self.num_blocks <= 0 or self.block_size <= 0:

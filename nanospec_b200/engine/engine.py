@@ -39,6 +39,8 @@ class Engine:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.runner, config.graph_buckets, config.record_logits)
+            if config.capture_at_start:
+                self.graphs.capture_all(max_requests)
         self._inflight = None  # a decode step that has been launched and not yet read
         self.d2h_bytes_last = 0
 

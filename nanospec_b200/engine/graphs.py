@@ -146,9 +146,12 @@ class DecodeGraphs:
     def can_run(self, batch: list[Scheduled]) -> bool:
         return (all(len(s.tokens) == 1 and s.samples for s in batch) and self.bucket_size(len(batch)) is not None)
 
-    def capture_all(self) -> None:
+    def capture_all(self, max_batch: int | None = None) -> None:
+        """Captures every bucket that a batch of up to `max_batch` requests can fall into."""
+        top = self.sizes[-1] if max_batch is None else (self.bucket_size(max_batch) or self.sizes[-1])
         for b in reversed(self.sizes):  # largest first: the shared pool is sized by the biggest
-            self._bucket(b)
+            if b <= top:
+                self._bucket(b)
 
     def _bucket(self, size: int) -> _Bucket:
         if size not in self.buckets:
