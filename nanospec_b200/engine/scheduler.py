@@ -62,6 +62,7 @@ class Request:
     gen: torch.Generator = None  # CPU generator seeded per request: draws do not depend on the batch
     logprobs: list[TokenInfo] = field(default_factory=list)
     step_logits: list = field(default_factory=list)  # only with EngineConfig.record_logits
+    peak_pages: list[int] | None = None  # the scheduler's note: most pages per cache group it can ever hold
 
     def __post_init__(self) -> None:
         self.gen = torch.Generator()
@@ -72,6 +73,15 @@ class Request:
 
     def tokens(self) -> list[int]:
         return self.prompt_ids + self.out_tokens
+
+    def token_slice(self, start: int, end: int) -> list[int]:
+        """tokens()[start:end] without building the whole list."""
+        n_prompt = len(self.prompt_ids)
+        if end <= n_prompt:
+            return self.prompt_ids[start:end]
+        if start >= n_prompt:
+            return self.out_tokens[start - n_prompt: end - n_prompt]
+        return self.prompt_ids[start:] + self.out_tokens[: end - n_prompt]
 
     @property
     def seq_len(self) -> int:
@@ -121,7 +131,10 @@ class Scheduler:
         return min(self.prefill_chunk, self.max_step_tokens)
 
     def _peak(self, req: Request) -> list[int]:
-        return self.cache.peak_pages(req.final_len, self._longest_portion())
+        # a request's final length and the longest portion do not change while it lives
+        if req.peak_pages is None:
+            req.peak_pages = self.cache.peak_pages(req.final_len, self._longest_portion())
+        return req.peak_pages
 
     def add(self, req: Request) -> None:
         assert req.state == "waiting"
@@ -142,16 +155,22 @@ class Scheduler:
         planned = [0] * len(cache.groups)  # pages this step's entries will take
         batch: list[Scheduled] = []
 
+        free = cache.free_pages()  # what this step may take: nothing is taken or given back while it is composed
+        # (a preemption gives pages back: `free` is read again after one)
+
+        need: list[int] = []  # of the request being looked at, as `fits` last computed it
+
         def fits(req_id: int | None, cur: int, n: int) -> bool:
+            nonlocal need
             need = cache.need(req_id, cur + n)
-            return all(nd + pl <= fr for nd, pl, fr in zip(need, planned, cache.free_pages()))
+            return all(nd + pl <= fr for nd, pl, fr in zip(need, planned, free))
 
         def plan(req: Request, n: int) -> None:
+            # follows a successful fits() for the same request and portion
             nonlocal budget
-            need = cache.need(req.id, req.committed + n)
             for i, nd in enumerate(need):
                 planned[i] += nd
-            toks = req.tokens()[req.committed: req.committed + n]
+            toks = req.token_slice(req.committed, req.committed + n)
             batch.append(Scheduled(req, toks, samples=(n == req.pending)))
             budget -= n
 
@@ -187,6 +206,7 @@ class Scheduler:
                         raise AssertionError("a single request does not fit in the pool")  # add() refuses these
                 unplan(victim)
                 self.preempt(victim)
+                free = cache.free_pages()
                 preempted = True
                 if victim is req:
                     n = 0
@@ -199,8 +219,7 @@ class Scheduler:
         headroom = None
         if preempted:
             return batch  # no admission in a step that had to give pages back
-        if self.admission == "reserve":
-            free = cache.free_pages()
+        if self.admission == "reserve" and self.waiting:
             owed = [0] * len(cache.groups)
             for r in self.running:
                 for gi, (pk, held) in enumerate(zip(self._peak(r), cache.held_pages(r.id))):
@@ -216,6 +235,7 @@ class Scheduler:
                 if any(p > h for p, h in zip(peak, headroom)):
                     break
                 headroom = [h - p for h, p in zip(headroom, peak)]
+                need = cache.need(None, n)
             elif not fits(None, 0, n):
                 break
             self.waiting.popleft()

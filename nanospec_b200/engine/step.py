@@ -117,12 +117,15 @@ class ModelRunner:
         N = sum(q_lens)
         ids_np = np.empty(N, dtype=np.int64)
         at = 0
-        for e in entries:
-            ids_np[at: at + len(e.tokens)] = e.tokens
-            at += len(e.tokens)
+        for e, n in zip(entries, q_lens):
+            if n == 1:
+                ids_np[at] = e.tokens[0]
+            else:
+                ids_np[at: at + n] = e.tokens
+            at += n
             for w in e.want:
-                if not 0 <= w < len(e.tokens):
-                    raise ValueError(f"request {e.req_id} wants logits at place {w} of {len(e.tokens)} tokens")
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.req_id} wants logits at place {w} of {n} tokens")
         if N and (ids_np.min() < 0 or ids_np.max() >= vocab):
             bad = int(ids_np[(ids_np < 0) | (ids_np >= vocab)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
@@ -130,10 +133,12 @@ class ModelRunner:
         self._reserve(entries)
 
         kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        q_lens_np = np.asarray(q_lens, dtype=np.int32)
         qo_indptr = np.zeros(B + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=qo_indptr[1:])
-        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)]) if N else np.zeros(0, np.int32)
-        token_req = np.repeat(np.arange(B, dtype=np.int32), q_lens)
+        np.cumsum(q_lens_np, out=qo_indptr[1:])
+        token_req = np.repeat(np.arange(B, dtype=np.int32), q_lens_np)
+        # token i of request b sits at position starts[b] + (i - qo_indptr[b])
+        positions = np.arange(N, dtype=np.int32) + np.repeat(np.asarray(starts, dtype=np.int32) - qo_indptr[:-1], q_lens_np)
         want_rows = [int(qo_indptr[b]) + w for b, e in enumerate(entries) for w in e.want]
         slots = [m.state_slot(e.req_id) for e in entries]
         tables, widths = [], []

@@ -24,7 +24,14 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"kernels exist for float32 and bfloat16, not {dt}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)  # the handle without a Stream object around it
+
+
 def _stream() -> int:
+    """The current CUDA stream of the current device, as the integer that the C ABI takes (asked for
+    at every launch, so that stream contexts and graph captures are followed)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
