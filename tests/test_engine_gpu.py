@@ -225,6 +225,36 @@ def test_eos_stops_and_is_kept(tiny_folders, tmp_path):
     assert eng.generate([prompt], params(max_tokens=8, ignore_eos=True)) == [greedy]
 
 
+def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
+    """Decode steps are launched before their predecessor's tokens have reached the host.  Requests
+    that end meanwhile (an end token, their own max_tokens) make the extra step run in vain: the
+    tokens are those of an engine that never looks ahead, with and without graphs, and every page
+    comes back."""
+    import json
+    import shutil
+
+    cfg, w = plain_model("B", tiny_folders["B"])
+    prompts = [random_ids(n, cfg["vocab"], seed=70 + n) for n in (6, 19, 33, 2)]
+    greedy = [plain.plain_greedy(cfg, w, p, 14)[0] for p in prompts]
+    folder = tmp_path / "ends"
+    shutil.copytree(tiny_folders["B"], folder)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [greedy[1][5]]}))
+    model = load(folder, torch.float32)
+    limits = [14, 14, 9, 3]
+    plist = [params(max_tokens=n) for n in limits]
+    want = []
+    for g, n in zip(greedy, limits):
+        g = g[:n]
+        stop = next((i + 1 for i, t in enumerate(g) if t == greedy[1][5]), len(g))
+        want.append(g[:stop])
+    assert len(want[1]) <= 6 and len({len(x) for x in want}) >= 3   # they end at different steps
+    for kw in (dict(cuda_graphs=True, lookahead=True), dict(cuda_graphs=True, lookahead=False), dict(cuda_graphs=False)):
+        eng = engine(model, num_blocks=40, block_size=8, **kw)
+        assert eng.generate(prompts, plist) == want, kw
+        eng.cache.check()
+        assert eng.cache.live == [] and all(f == 40 for f in eng.cache.free_pages()), kw
+
+
 def test_errors_are_loud(tiny_folders):
     from nanospec_b200.engine import RequestTooLarge
     model = load(tiny_folders["A"], torch.float32)
