@@ -50,6 +50,24 @@ NS_API int ns_embed(const void* table, const int* ids, float* out, int n_tokens,
 }
 
 // ---------------------------------------------------------------------------------------
+// token ids that an earlier step sampled and the host has not seen yet: ids[dst_rows[i]] = src[src_rows[i]]
+// ---------------------------------------------------------------------------------------
+__global__ void take_ids_kernel(int* __restrict__ ids, const int* __restrict__ dst_rows, const int* __restrict__ src,
+                                const int* __restrict__ src_rows, int n) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[dst_rows[i]] = src[src_rows[i]];
+}
+
+NS_API int ns_take_ids(int* ids, const int* dst_rows, const int* src, const int* src_rows, int n, cudaStream_t stream) {
+    if (n <= 0) return NS_OK;
+    NS_LAUNCH(take_ids_kernel, (n + 127) / 128, 128, 0, stream, ids, dst_rows, src, src_rows, n);
+    NS_CHECK_LAUNCH("ns_take_ids");
+    return NS_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // RMSNorm over the residual stream, with the pending branch output added first:
 //   r = resid[row] + branch[row]        (branch may be absent)
 //   resid[row] = r                      (when write_resid)

@@ -16,6 +16,7 @@ from .. import ops
 from ..config.engine import EngineConfig
 from ..parts.model import DecoderModel
 from .scheduler import Request, SamplingParams, Scheduled, Scheduler, TokenInfo
+from .graphs import InFlight
 from .step import ModelRunner, StepEntry
 
 
@@ -41,7 +42,10 @@ class Engine:
             self.graphs = DecodeGraphs(self.runner, config.graph_buckets, config.record_logits)
             if config.capture_at_start:
                 self.graphs.capture_all(max_requests)
-        self._inflight = None  # a decode step that has been launched and not yet read
+        self._inflight = None  # a step that has been launched and not yet read
+        self._score_bufs: list = [None, None]
+        self._score_turn = 0
+        self.launched_ahead = 0  # steps that were launched before their predecessor had been read
         self.d2h_bytes_last = 0
 
     # ---- profiling (CUDA events per phase, read once per step) -------------------------------
@@ -93,26 +97,64 @@ class Engine:
     def step(self) -> list[Request]:
         """Composes a batch, runs it, samples; returns the requests that finished.
 
-        Decode-only batches go through CUDA graphs.  While nothing else is waiting, the step after
-        such a batch is launched before this one's tokens have reached the host: it takes them on
-        the device, and the host's work (and the graph's launch latency) overlaps the GPU.  A request
-        that turns out to have ended meanwhile simply ignores the extra step's result."""
+        Decode-only batches of up to the largest bucket go through CUDA graphs.  While nothing is waiting
+        for admission, the step after this one is composed and launched before this one's tokens have
+        reached the host: it takes them on the device, and the host's work (composing the batch,
+        launching its kernels) overlaps the GPU.  A request that turns out to have ended meanwhile
+        simply ignores the extra step's result."""
         if self._inflight is None:
             batch = self.sched.next_batch()
             if not batch:
                 return []
             self._mark("start")
-            if self.graphs is None or not self.graphs.can_run(batch):
-                return self._run_eager(batch)
-            self._inflight = self._launch_decode(batch, ids_from_device=False)
+            self._inflight = self._launch(batch, None)
         flight = self._inflight
         ahead = None
-        if self._can_look_ahead(flight.batch):
-            ahead = self._launch_decode([Scheduled(s.req, [0], True) for s in flight.batch], ids_from_device=True)
-        tok, lpr, lpp, raw = self.graphs.collect(flight)
+        nxt = self._batch_ahead(flight)
+        if nxt is not None:
+            ahead = self._launch(nxt, flight)
+            self.launched_ahead += 1
+        finished = self._collect(flight)
+        self._inflight = ahead
+        self._after_step()
+        return finished
+
+    def _launch(self, batch: list[Scheduled], prev):
+        """Launches the step and returns a handle to collect it with.  `prev`: the step in flight whose
+        sampled tokens this one takes on the device (entries with `from_row`), or None."""
+        if self.graphs is not None and self.graphs.can_run(batch) and (prev is None or isinstance(prev, InFlight)):
+            flight = self.graphs.launch(batch, self._uniforms(batch), ids_from_device=prev is not None)
+            for s in batch:
+                s.req.committed += 1
+            return flight
+        sampling = [s for s in batch if s.samples]
+        entries = [StepEntry(s.req.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
+        take = None
+        if prev is not None:
+            dst, src, row = [], [], 0
+            for s in batch:
+                if s.from_row is not None:
+                    dst.append(row)
+                    src.append(s.from_row)
+                row += len(s.tokens)
+            take = (dst, prev.tok_dev, src)
+        hidden = self.runner.run(entries, take)
+        self._mark("forward")
+        for s in batch:
+            s.req.committed += len(s.tokens)
+        return self._score_launch(hidden, batch, sampling)
+
+    def _collect(self, flight) -> list[Request]:
+        """Waits for the step's tokens and hands them to their requests."""
+        if isinstance(flight, InFlight):
+            tok, lpr, lpp, raw = self.graphs.collect(flight)
+            sampling = flight.batch
+        else:
+            tok, lpr, lpp, raw = self._score_collect(flight)
+            sampling = flight.sampling
         self._mark("score")
         finished = []
-        for row, s in enumerate(flight.batch):
+        for row, s in enumerate(sampling):
             req = s.req
             if req.state != "running":
                 continue  # it ended in the step before; this step ran for it in vain
@@ -121,50 +163,69 @@ class Engine:
             if self._emit(req, TokenInfo(tok[row], lpr[row], lpp[row])):
                 self.sched.finish(req)
                 finished.append(req)
-        self._inflight = ahead
-        self._after_step()
         return finished
 
-    def _launch_decode(self, batch: list[Scheduled], ids_from_device: bool):
-        flight = self.graphs.launch(batch, self._uniforms(batch), ids_from_device)
-        for s in batch:
-            s.req.committed += 1
-        return flight
-
-    def _can_look_ahead(self, batch: list[Scheduled]) -> bool:
-        if not self.config.lookahead or self.config.record_logits or self.sched.waiting:
-            return False
-        for s in batch:
+    def _batch_ahead(self, flight) -> list[Scheduled] | None:
+        """The batch that follows the step in flight if every request that it samples for goes on, or
+        None when that cannot be said without its tokens (then the next step is composed by the
+        scheduler, after this one has been collected)."""
+        cfg = self.config
+        if not cfg.lookahead or cfg.record_logits or cfg.profile or self.sched.waiting:
+            return None
+        cache, running = self.cache, self.sched.running
+        if isinstance(flight, InFlight):
+            for s in flight.batch:
+                req = s.req
+                # still running after the step in flight, and room for one more position
+                if req.state != "running" or len(req.out_tokens) + 2 > req.params.max_tokens \
+                        or req.committed + 1 > self.runner.max_positions or not cache.can_extend(req.id, 1):
+                    return None
+            return [Scheduled(s.req, [0], True) for s in flight.batch]
+        # a step of portions and decode tokens: every running request is in it, in the scheduler's order
+        # (decoding ones first, then portions, each oldest first), and everything must fit
+        if len(flight.batch) != len(running) or any(s.req.state != "running" for s in flight.batch):
+            return None
+        row_of = {id(s): i for i, s in enumerate(flight.sampling)}
+        age = {id(r): i for i, r in enumerate(running)}
+        decoding, portions = [], []
+        for s in flight.batch:
             req = s.req
-            # still running after the step in flight, and room for one more position
-            if req.state != "running" or len(req.out_tokens) + 2 > req.params.max_tokens \
-                    or req.committed + 1 > self.runner.max_positions or not self.cache.can_extend(req.id, 1):
-                return False
-        return True
-
-    def _run_eager(self, batch: list[Scheduled]) -> list[Request]:
-        sampling = [s for s in batch if s.samples]
-        entries = [StepEntry(s.req.id, s.tokens, [len(s.tokens) - 1] if s.samples else []) for s in batch]
-        hidden = self.runner.run(entries)
-        self._mark("forward")
-        tok, lpr, lpp, raw = self._score(hidden, sampling)
-        self._mark("score")
-        finished = []
-        row = 0
-        for s in batch:
-            req = s.req
-            req.committed += len(s.tokens)
+            if id(req) not in age:
+                return None
             if not s.samples:
-                continue
-            if raw is not None:
-                req.step_logits.append(raw[row])
-            done = self._emit(req, TokenInfo(tok[row], lpr[row], lpp[row]))
-            row += 1
-            if done:
-                self.sched.finish(req)
-                finished.append(req)
-        self._after_step()
-        return finished
+                portions.append(req)
+            elif len(req.out_tokens) + 1 < req.params.max_tokens:  # else it ends with the step in flight
+                if req.committed + 1 > self.runner.max_positions:
+                    return None
+                decoding.append(Scheduled(req, [0], True, from_row=row_of[id(s)]))
+        decoding.sort(key=lambda sch: age[id(sch.req)])
+        portions.sort(key=lambda r: age[id(r)])
+        budget = cfg.max_step_tokens
+        free, planned = cache.free_pages(), [0] * len(cache.groups)
+
+        def fits(req: Request, n: int) -> bool:
+            need = cache.need(req.id, req.committed + n)
+            if any(nd + pl > fr for nd, pl, fr in zip(need, planned, free)):
+                return False
+            for i, nd in enumerate(need):
+                planned[i] += nd
+            return True
+
+        out: list[Scheduled] = []
+        for sch in decoding:
+            if budget <= 0 or not fits(sch.req, 1):
+                return None
+            out.append(sch)
+            budget -= 1
+        for req in portions:
+            n = min(req.pending, cfg.prefill_chunk, budget)
+            if n <= 0 or not fits(req, n):
+                return None
+            out.append(Scheduled(req, req.token_slice(req.committed, req.committed + n), samples=(n == req.pending)))
+            budget -= n
+        if not out or (self.graphs is not None and self.graphs.can_run(out)):
+            return None  # nothing left, or a batch for the graphs: they take over after a step composed in the usual way
+        return out
 
     def _after_step(self) -> None:
         self.steps += 1
@@ -177,10 +238,25 @@ class Engine:
         # the reference): results do not depend on what else is in the batch
         return [float(torch.rand(1, generator=s.req.gen)) if s.req.params.temperature > 0 else 0.0 for s in sampling]
 
-    def _score(self, hidden: torch.Tensor | None, sampling: list[Scheduled]):
-        """Head projection and token choice for the rows of `hidden`, `head_chunk` rows at a time."""
+    def _score_buffers(self, rows: int):
+        """Device and pinned host buffers for a step's sampled tokens and log-probs; two sets used in turn
+        (a step launched ahead writes its own while the one before it is still to be read)."""
+        self._score_turn ^= 1
+        bufs = self._score_bufs[self._score_turn]
+        if bufs is None or bufs[0].numel() < rows:
+            cap = max(256, 2 * rows)
+            dev = self.device
+            bufs = (torch.zeros(cap, dtype=torch.int32, device=dev), torch.zeros(2, cap, dtype=torch.float32, device=dev),
+                    torch.zeros(cap, dtype=torch.int32).pin_memory(), torch.zeros(2, cap, dtype=torch.float32).pin_memory(),
+                    torch.cuda.Event())
+            self._score_bufs[self._score_turn] = bufs
+        return bufs
+
+    def _score_launch(self, hidden: torch.Tensor | None, batch: list[Scheduled], sampling: list[Scheduled]) -> "EagerFlight":
+        """Head projection and token choice for the rows of `hidden`, `head_chunk` rows at a time; the
+        results start their way to the host and are read by `_score_collect`."""
         if hidden is None or not sampling:
-            return [], [], [], None
+            return EagerFlight(batch, [], None, None, None, None, None)
         R = hidden.shape[0]
         dev = self.device
         P = [s.req.params for s in sampling]
@@ -188,7 +264,7 @@ class Engine:
         top_k = torch.tensor([p.top_k for p in P], dtype=torch.int32).to(dev, non_blocking=True)
         top_p = torch.tensor([p.top_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
         u = torch.tensor(self._uniforms(sampling), dtype=torch.float32).to(dev, non_blocking=True)
-        out = torch.empty((3, R), dtype=torch.float32, device=dev)
+        tok_dev, lp_dev, tok_host, lp_host, done = self._score_buffers(R)
         raw = [] if self.config.record_logits else None
         chunk = self.config.head_chunk
         logits_buf = self.runner.workspace.get("logits", min(chunk, R), self.model.vocab_size, torch.float32)
@@ -197,11 +273,24 @@ class Engine:
             z = self.model.logits(hidden[s:e], logits_buf[: e - s])
             if raw is not None:
                 raw.append(z.cpu())
-            tok, lpr, lpp = ops.sample_rows(z, temp[s:e], top_k[s:e], top_p[s:e], u[s:e])
-            out[0, s:e] = tok
-            out[1, s:e] = lpr
-            out[2, s:e] = lpp
-        vals = out.cpu()  # the step's one device-to-host read
-        self.d2h_bytes_last = vals.numel() * 4
-        tok = [int(x) for x in vals[0].tolist()]
-        return tok, vals[1].tolist(), vals[2].tolist(), (torch.cat(raw) if raw else None)
+            ops.sample_rows(z, temp[s:e], top_k[s:e], top_p[s:e], u[s:e], out=(tok_dev[s:e], lp_dev[0, s:e], lp_dev[1, s:e]))
+        tok_host[:R].copy_(tok_dev[:R], non_blocking=True)   # the step's device-to-host read: tokens and two log-probs per row
+        lp_host[:, :R].copy_(lp_dev[:, :R], non_blocking=True)
+        done.record()
+        self.d2h_bytes_last = R * 12
+        return EagerFlight(batch, sampling, tok_dev, tok_host, lp_host, done, torch.cat(raw) if raw else None)
+
+    def _score_collect(self, flight: "EagerFlight"):
+        if not flight.sampling:
+            return [], [], [], None
+        R = len(flight.sampling)
+        flight.done.synchronize()
+        return flight.tok_host[:R].tolist(), flight.lp_host[0, :R].tolist(), flight.lp_host[1, :R].tolist(), flight.raw
+
+
+class EagerFlight:
+    """A step of portions and decode tokens that has been launched and whose results have not been read yet."""
+
+    def __init__(self, batch, sampling, tok_dev, tok_host, lp_host, done, raw) -> None:
+        self.batch, self.sampling = batch, sampling
+        self.tok_dev, self.tok_host, self.lp_host, self.done, self.raw = tok_dev, tok_host, lp_host, done, raw

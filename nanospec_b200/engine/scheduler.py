@@ -105,6 +105,7 @@ class Scheduled:
     req: Request
     tokens: list[int]
     samples: bool  # the portion ends at the request's last known token: its last logits give the next token
+    from_row: int | None = None  # the one token is still on the device: row of the step before among its sampled rows
 
 
 class RequestTooLarge(ValueError):

@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import CacheManager, CacheStorage, PoolExhausted
 from ..parts.context import StepContext, Workspace
 from ..parts.model import DecoderModel
@@ -104,9 +105,12 @@ class ModelRunner:
                 self.manager.rollback(rid, before)
             raise
 
-    def build_context(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor | None, int]:
+    def build_context(self, entries: list[StepEntry], take: tuple[list[int], torch.Tensor, list[int]] | None = None,
+                      ) -> tuple[StepContext, torch.Tensor | None, int]:
         """Reserves pages, lays the step description out in one pinned buffer and copies it
-        to the device once.  Returns (context, wanted rows on the device or None, n wanted)."""
+        to the device once.  Returns (context, wanted rows on the device or None, n wanted).
+        `take` = (token rows of this step, an int32 device tensor, rows of it): those token ids are not
+        known to the host yet and are taken from the tensor on the device (the entries carry a placeholder)."""
         ids = [e.req_id for e in entries]
         if len(set(ids)) != len(ids):
             raise ValueError("a request may appear once in a step")
@@ -151,8 +155,10 @@ class ModelRunner:
             tables.append(table.reshape(-1))
             widths.append(width)
 
+        take_dst = np.asarray(take[0] if take else [], dtype=np.int32)
+        take_src = np.asarray(take[2] if take else [], dtype=np.int32)
         parts = [ids_np.astype(np.int32), positions, token_req, qo_indptr, np.asarray(kv_lens, dtype=np.int32),
-                 np.asarray(slots, dtype=np.int32), np.asarray(want_rows, dtype=np.int32), *tables]
+                 np.asarray(slots, dtype=np.int32), np.asarray(want_rows, dtype=np.int32), take_dst, take_src, *tables]
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
@@ -171,7 +177,9 @@ class ModelRunner:
         def view(i: int, n: int) -> torch.Tensor:
             return dev[offsets[i]: offsets[i] + n]
 
-        group_tables = [view(7 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
+        if take and len(take_dst):
+            ops.take_ids(view(0, N), view(7, len(take_dst)), take[1], view(8, len(take_src)))
+        group_tables = [view(9 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
         self.storage.zero_state_slots(m.take_fresh_slots())
         ctx = StepContext(
             n_tokens=N, n_requests=B,
@@ -186,10 +194,11 @@ class ModelRunner:
         return ctx, (view(6, n_want) if n_want else None), n_want
 
     # ---- running ------------------------------------------------------------------------
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def run(self, entries: list[StepEntry], take=None) -> torch.Tensor | None:
         """Runs the step and returns the normed hidden states at the wanted places, in the
-        order of the entries and of their `want` lists ([n_wanted, hidden]), or None."""
-        ctx, want_rows, n_want = self.build_context(entries)
+        order of the entries and of their `want` lists ([n_wanted, hidden]), or None.
+        `take`: token ids that are still on the device (see build_context)."""
+        ctx, want_rows, n_want = self.build_context(entries, take)
         hidden = self.model.forward(ctx, want_rows)  # None when nothing is wanted: the blocks still fill the cache
         for e in entries:
             self.manager.trim(e.req_id)

@@ -64,6 +64,16 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
+def take_ids(ids: torch.Tensor, dst_rows: torch.Tensor, src: torch.Tensor, src_rows: torch.Tensor) -> None:
+    """ids[dst_rows[i]] = src[src_rows[i]]: a step takes, on the device, the tokens that the step before it sampled."""
+    _cuda(ids, dst_rows, src, src_rows)
+    for t, name in ((ids, "ids"), (dst_rows, "dst_rows"), (src, "src"), (src_rows, "src_rows")):
+        _i32(t, name)
+    if dst_rows.numel() != src_rows.numel():
+        raise KernelError("take_ids: one source row per destination row")
+    lib.call("ns_take_ids", ids.data_ptr(), dst_rows.data_ptr(), src.data_ptr(), src_rows.data_ptr(), dst_rows.numel(), _stream())
+
+
 def add_rmsnorm(resid: torch.Tensor, branch: torch.Tensor | None, gain: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: torch.Tensor | None = None, write_resid: bool = True) -> torch.Tensor:
     """resid (+= branch); out = rmsnorm(resid) * gain.  With `rows`, output row j reads

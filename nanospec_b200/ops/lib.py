@@ -23,6 +23,7 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES: dict[str, list] = {
     "ns_embed": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "ns_take_ids": [_P, _P, _P, _P, _I, _P],
     "ns_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "ns_residual_add": [_P, _P, _I, _I, _I, _P],
     "ns_swiglu": [_P, _P, _I, _I, _I, _I, _P],

@@ -226,7 +226,7 @@ def test_eos_stops_and_is_kept(tiny_folders, tmp_path):
 
 
 def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
-    """Decode steps are launched before their predecessor's tokens have reached the host.  Requests
+    """Steps are launched before their predecessor's tokens have reached the host.  Requests
     that end meanwhile (an end token, their own max_tokens) make the extra step run in vain: the
     tokens are those of an engine that never looks ahead, with and without graphs, and every page
     comes back."""
@@ -248,11 +248,18 @@ def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
         stop = next((i + 1 for i, t in enumerate(g) if t == greedy[1][5]), len(g))
         want.append(g[:stop])
     assert len(want[1]) <= 6 and len({len(x) for x in want}) >= 3   # they end at different steps
-    for kw in (dict(cuda_graphs=True, lookahead=True), dict(cuda_graphs=True, lookahead=False), dict(cuda_graphs=False)):
+    for kw in (dict(cuda_graphs=True, lookahead=True), dict(cuda_graphs=True, lookahead=False),
+               dict(cuda_graphs=False, lookahead=True), dict(cuda_graphs=False, lookahead=False),
+               # portions of prompts beside decode tokens, launched ahead as well
+               dict(cuda_graphs=False, lookahead=True, prefill_chunk=7, max_admit=1),
+               dict(cuda_graphs=True, lookahead=True, prefill_chunk=5, max_step_tokens=9),
+               dict(cuda_graphs=False, lookahead=False, prefill_chunk=7, max_admit=1)):
         eng = engine(model, num_blocks=40, block_size=8, **kw)
         assert eng.generate(prompts, plist) == want, kw
         eng.cache.check()
         assert eng.cache.live == [] and all(f == 40 for f in eng.cache.free_pages()), kw
+        if kw.get("lookahead") and not kw["cuda_graphs"]:
+            assert eng.launched_ahead > 0, kw
 
 
 def test_errors_are_loud(tiny_folders):
