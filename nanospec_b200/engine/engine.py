@@ -97,11 +97,13 @@ class Engine:
     def step(self) -> list[Request]:
         """Composes a batch, runs it, samples; returns the requests that finished.
 
-        Decode-only batches of up to the largest bucket go through CUDA graphs.  While nothing is waiting
-        for admission, the step after this one is composed and launched before this one's tokens have
+        Decode-only batches of up to the largest bucket go through CUDA graphs.  While nobody can be
+        admitted, the step after this one is composed and launched before this one's tokens have
         reached the host: it takes them on the device, and the host's work (composing the batch,
         launching its kernels) overlaps the GPU.  A request that turns out to have ended meanwhile
         simply ignores the extra step's result."""
+        if self._inflight is not None and not any(s.req.state == "running" for s in self._inflight.batch):
+            self._inflight = None  # a step launched ahead for requests that have all ended meanwhile: nothing to read
         if self._inflight is None:
             batch = self.sched.next_batch()
             if not batch:
@@ -122,8 +124,9 @@ class Engine:
     def _launch(self, batch: list[Scheduled], prev):
         """Launches the step and returns a handle to collect it with.  `prev`: the step in flight whose
         sampled tokens this one takes on the device (entries with `from_row`), or None."""
-        if self.graphs is not None and self.graphs.can_run(batch) and (prev is None or isinstance(prev, InFlight)):
-            flight = self.graphs.launch(batch, self._uniforms(batch), ids_from_device=prev is not None)
+        if self.graphs is not None and self.graphs.can_run(batch):
+            take = None if prev is None else (prev.tok_dev, [s.from_row for s in batch])
+            flight = self.graphs.launch(batch, self._uniforms(batch), take)
             for s in batch:
                 s.req.committed += 1
             return flight
@@ -170,18 +173,10 @@ class Engine:
         None when that cannot be said without its tokens (then the next step is composed by the
         scheduler, after this one has been collected)."""
         cfg = self.config
-        if not cfg.lookahead or cfg.record_logits or cfg.profile or self.sched.waiting:
-            return None
+        if not cfg.lookahead or cfg.record_logits or cfg.profile or self.sched.could_admit():
+            return None  # (somebody who waits and cannot be admitted as things stand waits one step longer at most)
         cache, running = self.cache, self.sched.running
-        if isinstance(flight, InFlight):
-            for s in flight.batch:
-                req = s.req
-                # still running after the step in flight, and room for one more position
-                if req.state != "running" or len(req.out_tokens) + 2 > req.params.max_tokens \
-                        or req.committed + 1 > self.runner.max_positions or not cache.can_extend(req.id, 1):
-                    return None
-            return [Scheduled(s.req, [0], True) for s in flight.batch]
-        # a step of portions and decode tokens: every running request is in it, in the scheduler's order
+        # every running request is in the step in flight; the next batch has them in the scheduler's order
         # (decoding ones first, then portions, each oldest first), and everything must fit
         if len(flight.batch) != len(running) or any(s.req.state != "running" for s in flight.batch):
             return None
@@ -223,9 +218,7 @@ class Engine:
                 return None
             out.append(Scheduled(req, req.token_slice(req.committed, req.committed + n), samples=(n == req.pending)))
             budget -= n
-        if not out or (self.graphs is not None and self.graphs.can_run(out)):
-            return None  # nothing left, or a batch for the graphs: they take over after a step composed in the usual way
-        return out
+        return out or None
 
     def _after_step(self) -> None:
         self.steps += 1
@@ -274,8 +267,11 @@ class Engine:
             if raw is not None:
                 raw.append(z.cpu())
             ops.sample_rows(z, temp[s:e], top_k[s:e], top_p[s:e], u[s:e], out=(tok_dev[s:e], lp_dev[0, s:e], lp_dev[1, s:e]))
-        tok_host[:R].copy_(tok_dev[:R], non_blocking=True)   # the step's device-to-host read: tokens and two log-probs per row
-        lp_host[:, :R].copy_(lp_dev[:, :R], non_blocking=True)
+        # the step's device-to-host read: tokens and two log-probs per row (each copy contiguous: a strided copy
+        # between device and host goes through a temporary and blocks the host)
+        tok_host[:R].copy_(tok_dev[:R], non_blocking=True)
+        lp_host[0, :R].copy_(lp_dev[0, :R], non_blocking=True)
+        lp_host[1, :R].copy_(lp_dev[1, :R], non_blocking=True)
         done.record()
         self.d2h_bytes_last = R * 12
         return EagerFlight(batch, sampling, tok_dev, tok_host, lp_host, done, torch.cat(raw) if raw else None)

@@ -35,7 +35,7 @@ class _Bucket:
         m = runner.manager
         n_groups = len(m.groups)
         names = ["positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
-                 "temperature", "top_p", "u"]
+                 "temperature", "top_p", "u", "take_dst", "take_src"]
         self.off: dict[str, int] = {}
         total = 0
         for nm in names:
@@ -51,14 +51,17 @@ class _Bucket:
         self.host_f32 = self.host.view(torch.float32).numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
         # token ids live apart from the rest: a step launched ahead of its predecessor's results takes
-        # them on the device, from the predecessor's sampled tokens
+        # them on the device, from the predecessor's sampled tokens (`out_token` of a bucket, or an eager step's)
         self.ids_host = torch.full((size,), -1, dtype=torch.int32).pin_memory()
         self.ids_dev = torch.full((size,), -1, dtype=torch.int32, device=runner.device)
         self.row_sig: list[tuple | None] = [None] * size
         self.copied = torch.cuda.Event()
         self.out_token = torch.zeros(size, dtype=torch.int32, device=runner.device)
         self.out_lp = torch.zeros(2, size, dtype=torch.float32, device=runner.device)
-        self.out_host = [torch.zeros(3, size, dtype=torch.float32).pin_memory() for _ in range(2)]  # used in turn
+        # results on the host, two sets used in turn.  They are copied whole: a copy of part of each row is not
+        # contiguous, and such a copy between device and host goes through a temporary and blocks the host
+        self.tok_host = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.lp_host = [torch.zeros(2, size, dtype=torch.float32).pin_memory() for _ in range(2)]
         self.out_done = [torch.cuda.Event(), torch.cuda.Event()]
         self.turn = 0
         self.logits = torch.zeros(size, runner.model.vocab_size, dtype=torch.float32, device=runner.device)
@@ -162,16 +165,17 @@ class DecodeGraphs:
         """launch() and collect() in one: (tokens, raw log-probs, processed log-probs, logits rows or None)."""
         return self.collect(self.launch(batch, uniforms))
 
-    def launch(self, batch: list[Scheduled], uniforms: list[float], ids_from_device: bool = False) -> "InFlight":
+    def launch(self, batch: list[Scheduled], uniforms: list[float], take: tuple[torch.Tensor, list[int]] | None = None,
+               ) -> "InFlight":
         """Reserves pages, fills the bucket's description, copies it and replays the graph; does not
-        wait.  With `ids_from_device` the step's token ids are the tokens that the bucket's previous
-        replay sampled (same requests in the same rows): the step can be launched before those tokens
-        have reached the host."""
+        wait.  With `take` = (int32 device tensor, one row of it per request) the step's token ids are
+        tokens that an earlier step sampled and that the host has not seen: the step can be launched
+        before they have reached it."""
         runner = self.runner
         m = runner.manager
         B = len(batch)
         bk = self._bucket(self.bucket_size(B))
-        entries = [StepEntry(s.req.id, [0] if ids_from_device else s.tokens, [0]) for s in batch]
+        entries = [StepEntry(s.req.id, [0] if take is not None else s.tokens, [0]) for s in batch]
         starts = [m.seq_len[e.req_id] for e in entries]
         runner._reserve(entries)
         bk.copied.synchronize()  # the previous copy out of the pinned buffers has finished
@@ -199,22 +203,25 @@ class DecodeGraphs:
         if self.timing is not None:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
-        if ids_from_device:
-            bk.ids_dev[:B].copy_(bk.out_token[:B])  # rows beyond B still hold the padding id of the launch before
+        if take is not None:
+            bk.ids_host[:B] = 0
+            hn[o["take_dst"]: o["take_dst"] + B] = np.arange(B, dtype=np.int32)
+            hn[o["take_src"]: o["take_src"] + B] = take[1]
         else:
             bk.ids_host[:B] = torch.tensor([s.tokens[0] for s in batch], dtype=torch.int32)
-            bk.ids_dev.copy_(bk.ids_host, non_blocking=True)
+        bk.ids_dev.copy_(bk.ids_host, non_blocking=True)  # padding rows carry -1
         bk.dev.copy_(bk.host, non_blocking=True)
         bk.copied.record()
-        runner.h2d_bytes_last = bk.total * 4 + (0 if ids_from_device else bk.size * 4)
+        if take is not None:
+            ops.take_ids(bk.ids_dev, bk.dev[o["take_dst"]: o["take_dst"] + B], take[0], bk.dev[o["take_src"]: o["take_src"] + B])
+        runner.h2d_bytes_last = (bk.total + bk.size) * 4
         runner.storage.zero_state_slots(m.take_fresh_slots())
         bk.graph.replay()
         self.replays += 1
         turn = bk.turn
         bk.turn ^= 1
-        out_host = bk.out_host[turn]
-        out_host[0, :B].copy_(bk.out_token[:B], non_blocking=True)
-        out_host[1:, :B].copy_(bk.out_lp[:, :B], non_blocking=True)
+        bk.tok_host[turn].copy_(bk.out_token, non_blocking=True)
+        bk.lp_host[turn].copy_(bk.out_lp, non_blocking=True)
         raw = bk.logits[:B].cpu() if self.record_logits else None
         bk.out_done[turn].record()
         if t1 is not None:
@@ -228,9 +235,8 @@ class DecodeGraphs:
         """Waits for a launched step's results: (tokens, raw log-probs, processed log-probs, logits or None)."""
         bk, B = flight.bucket, flight.n
         bk.out_done[flight.turn].synchronize()
-        out = bk.out_host[flight.turn]
-        tok = [int(x) for x in out[0, :B].tolist()]
-        return tok, out[1, :B].tolist(), out[2, :B].tolist(), flight.raw
+        lp = bk.lp_host[flight.turn]
+        return bk.tok_host[flight.turn][:B].tolist(), lp[0, :B].tolist(), lp[1, :B].tolist(), flight.raw
 
 
 class InFlight:
@@ -238,3 +244,5 @@ class InFlight:
 
     def __init__(self, batch: list[Scheduled], bucket: _Bucket, turn: int, n: int, raw) -> None:
         self.batch, self.bucket, self.turn, self.n, self.raw = batch, bucket, turn, n, raw
+        self.sampling = batch            # every row samples
+        self.tok_dev = bucket.out_token  # where the sampled tokens lie until the bucket's next replay

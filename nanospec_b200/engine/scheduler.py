@@ -247,6 +247,28 @@ class Scheduler:
             admitted += 1
         return batch
 
+    def could_admit(self) -> bool:
+        """Whether `next_batch` would admit the head of the queue as things stand now (live requests,
+        state slots, pages).  The engine asks before it launches a step ahead of its predecessor's
+        results: while nobody can be admitted anyway, the next batch does not depend on them."""
+        if not self.waiting:
+            return False
+        if self.max_running is not None and len(self.running) >= self.max_running:
+            return False
+        cache = self.cache
+        if cache.slots.num_free <= 0:
+            return False
+        req = self.waiting[0]
+        free = cache.free_pages()
+        if self.admission == "reserve":
+            owed = [0] * len(cache.groups)
+            for r in self.running:
+                for gi, (pk, held) in enumerate(zip(self._peak(r), cache.held_pages(r.id))):
+                    owed[gi] += max(0, pk - held)
+            return all(p <= f - o for p, f, o in zip(self._peak(req), free, owed))
+        n = min(req.pending, self.prefill_chunk, self.max_step_tokens)
+        return all(nd <= fr for nd, fr in zip(cache.need(None, n), free))
+
     # ---- transitions -----------------------------------------------------------------------
     def finish(self, req: Request) -> None:
         self.running.remove(req)

@@ -262,6 +262,26 @@ def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
             assert eng.launched_ahead > 0, kw
 
 
+def test_a_step_launched_for_requests_that_are_gone_costs_no_call(tiny_folders):
+    """Requests taken away while a step launched ahead for them is in flight: the next call of `step`
+    does not spend itself on reading that step, it runs what is there to run."""
+    cfg, w = plain_model("A", tiny_folders["A"])
+    model = load(tiny_folders["A"], torch.float32)
+    for graphs in (True, False):
+        eng = engine(model, cuda_graphs=graphs)
+        olds = [eng.add(random_ids(n, cfg["vocab"], seed=n), params(max_tokens=50, ignore_eos=True)) for n in (4, 9)]
+        for _ in range(5):
+            eng.step()
+        assert eng.launched_ahead > 0 and eng._inflight is not None
+        for r in olds:
+            eng.sched.finish(r)
+        prompt = random_ids(11, cfg["vocab"], seed=3)
+        new = eng.add(prompt, params(max_tokens=1))
+        assert eng.step() == [new] and new.out_tokens == plain.plain_greedy(cfg, w, prompt, 1)[0]
+        eng.cache.check()
+        assert eng.cache.live == []
+
+
 def test_errors_are_loud(tiny_folders):
     from nanospec_b200.engine import RequestTooLarge
     model = load(tiny_folders["A"], torch.float32)
