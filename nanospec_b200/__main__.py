@@ -35,6 +35,7 @@ def _engine_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--admission", choices=["reserve", "optimistic"], default="reserve")
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--no-lookahead", action="store_true", help="never launch a step before the one before it has been read")
 
 
 def _load(args):
@@ -55,7 +56,7 @@ def _engine(model, args, num_blocks: int):
     return Engine(model, EngineConfig(
         num_blocks=args.num_blocks or num_blocks, block_size=args.block_size, max_admit=args.max_admit,
         max_running=args.max_running, cuda_graphs=not args.no_cuda_graphs, max_step_tokens=args.max_step_tokens,
-        prefill_chunk=args.prefill_chunk, admission=args.admission))
+        prefill_chunk=args.prefill_chunk, admission=args.admission, lookahead=not args.no_lookahead))
 
 
 def cmd_generate(args) -> int:
@@ -150,7 +151,7 @@ def cmd_profile(args) -> int:
     cfg = LlamaConfig(**sh, num_hidden_layers=layers, rms_norm_eps=1e-5, rope_theta=500000.0,
                       max_position_embeddings=max(8192, args.context + 512), rope_scaling=Llama3RopeScaling(factor, 1.0, 4.0, 8192))
     model = random_model(cfg, seed=0, device="cuda", dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
-    if args.what in ("batch", "mixed"):
+    if args.what in ("batch", "mixed", "queue"):
         return _profile_workload(args, cfg, model)
     args.max_running = max(args.batch, 1)
     args.max_admit = 64
@@ -213,7 +214,8 @@ def cmd_profile(args) -> int:
 
 
 def _profile_workload(args, cfg, model) -> int:
-    """`batch`: continuous batching of --batch requests with prompt lengths uniform in [--prompt-min, --context] and
+    """`queue`: --requests requests through --batch live slots, so that somebody always waits.
+    `batch`: continuous batching of --batch requests with prompt lengths uniform in [--prompt-min, --context] and
     --new-tokens new tokens each.  `mixed`: --long prompts of --context tokens prefilled in portions of
     --prefill-chunk beside --batch requests that decode (temperature 1.0, fixed seeds)."""
     import time
@@ -224,6 +226,28 @@ def _profile_workload(args, cfg, model) -> int:
 
     g = torch.Generator().manual_seed(0)
     bs = args.block_size
+    if args.what == "queue":
+        n_req = args.requests or 3 * args.batch
+        lens = torch.randint(args.prompt_min, args.context + 1, (n_req,), generator=g).tolist()
+        news = torch.randint(max(1, args.new_tokens // 4), args.new_tokens + 1, (n_req,), generator=g).tolist()
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+        args.max_running, args.max_admit = args.batch, 64
+        runs = []
+        for _ in range(2):  # the second run is the one that counts: the first also warms the library's kernels up
+            engine = _engine(model, args, args.batch * (-(-(args.context + args.new_tokens) // bs) + 1) + 16)
+            for p, n in zip(prompts, news):
+                engine.add(p, SamplingParams(max_tokens=n, ignore_eos=True))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            while engine.sched.has_work:
+                engine.step()
+            torch.cuda.synchronize()
+            runs.append(time.perf_counter() - t0)
+        dt = runs[-1]
+        print(json.dumps({"what": "queue", "shape": args.shape, "requests": n_req, "live": args.batch, "prompt_tokens": sum(lens),
+                          "new_tokens": sum(news), "seconds": round(dt, 3), "steps": engine.steps, "launched_ahead": engine.launched_ahead,
+                          "new_tokens_per_s": round(sum(news) / dt, 1)}), flush=True)
+        return 0
     if args.what == "batch":
         lens = torch.randint(args.prompt_min, args.context + 1, (args.batch,), generator=g).tolist()
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
@@ -320,12 +344,15 @@ def main(argv: list[str] | None = None) -> int:
     pr.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (smaller captures)")
     pr.add_argument("--batch", type=int, default=8)
     pr.add_argument("--context", type=int, default=1024)
-    pr.add_argument("--what", choices=["decode", "prefill", "batch", "mixed"], default="decode",
+    pr.add_argument("--what", choices=["decode", "prefill", "batch", "mixed", "queue"], default="decode",
                     help="decode steps; the prefill of --batch prompts; batch: continuous batching of --batch requests; "
                          "mixed: --long prompts prefilled in portions beside --batch decoding requests")
     pr.add_argument("--prompt-min", type=int, default=16, help="batch: shortest prompt (the longest is --context)")
     pr.add_argument("--new-tokens", type=int, default=256, help="batch: new tokens per request")
     pr.add_argument("--long", type=int, default=8, help="mixed: number of long prompts")
+    pr.add_argument("--requests", type=int, default=None,
+                    help="queue: requests in all (default 3 x --batch), through --batch live slots; prompts of --prompt-min to "
+                         "--context tokens, --new-tokens / 4 to --new-tokens new ones")
     pr.add_argument("--steps", type=int, default=1, help="decode steps to time (the median is printed)")
     pr.set_defaults(fn=cmd_profile)
 
