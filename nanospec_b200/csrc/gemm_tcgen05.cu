@@ -98,6 +98,20 @@ __device__ __forceinline__ void store_out2(float* p, float a, float b) { *reinte
 __device__ __forceinline__ void store_out2(__nv_bfloat16* p, float a, float b) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
+// four neighbouring outputs: one store where the address allows it
+__device__ __forceinline__ void store_out4(float* p, const float4& v) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) *reinterpret_cast<float4*>(p) = v;
+    else { p[0] = v.x; p[1] = v.y; p[2] = v.z; p[3] = v.w; }
+}
+__device__ __forceinline__ void store_out4(__nv_bfloat16* p, const float4& v) {
+    if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+        p[0] = __float2bfloat16_rn(v.x); p[1] = __float2bfloat16_rn(v.y);
+        p[2] = __float2bfloat16_rn(v.z); p[3] = __float2bfloat16_rn(v.w);
+    }
+}
 
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, Cfg<BN>::kMinBlocks)
@@ -135,7 +149,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int kb_begin = split * per + min(split, rem);
     const int kb_count = per + (split < rem ? 1 : 0);
 
-    float rope_sin0 = 0.f, rope_cos0 = 1.f;  // rope mode: sine and cosine of a thread's first (token, pair)
+    // rope mode: what a thread needs for its first (token, four pairs) of the reduction below, fetched while the product runs
+    float rope_sin0[4] = {0.f, 0.f, 0.f, 0.f}, rope_cos0[4] = {1.f, 1.f, 1.f, 1.f};
+    int rope_req0 = -1, rope_pos0 = 0, rope_page0 = 0;
     if (threadIdx.x == 0) {
         failed = 0;
         for (int s = 0; s < C::kStages; ++s) {
@@ -226,39 +242,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;  // the TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;
         if (kNorm) {
-            // While the products run: each token's scale.  A warp takes a token at a time, a lane every 32nd
-            // partial sum (all of a lane's loads are requested before the first is used), then the lanes'
+            // While the products run: each token's scale.  A warp takes four tokens at a time, a lane every 32nd
+            // partial sum of each (the loads of all four are requested before the first is used), then the lanes'
             // sums are added in a fixed tree: the same value in every block, whatever the timing.
-            for (int t = warp - 2; t < BN; t += 4) {
-                float inv = 1.f;
-                if (ep.row_partials && tok0 + t < M_tok) {
-                    const float* p = ep.row_partials + (size_t)(tok0 + t) * ep.n_partials;
-                    float acc = 0.f;
+            for (int t0 = warp - 2; t0 < BN; t0 += 16) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                if (ep.row_partials) {
                     for (int i0 = 0; i0 < ep.n_partials; i0 += 256) {
-                        float v[8];
+                        float v[4][8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const int i = i0 + lane + 32 * k;
-                            v[k] = i < ep.n_partials ? __ldg(p + i) : 0.f;
+                        for (int u = 0; u < 4; ++u) {
+                            const int t = t0 + 4 * u;
+                            const bool live = t < BN && tok0 + t < M_tok;
+                            const float* p = ep.row_partials + (size_t)(live ? tok0 + t : 0) * ep.n_partials;
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const int i = i0 + lane + 32 * k;
+                                v[u][k] = live && i < ep.n_partials ? __ldg(p + i) : 0.f;
+                            }
                         }
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) acc += v[k];
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) acc[u] += v[u][k];
                     }
-                    inv = rsqrtf(ns_warp_sum(acc) * ep.inv_hidden + ep.eps);
                 }
-                if (lane == 0) inv_s[t] = inv;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int t = t0 + 4 * u;
+                    if (t >= BN) break;  // uniform across the warp
+                    float inv = 1.f;
+                    if (ep.row_partials && tok0 + t < M_tok) inv = rsqrtf(ns_warp_sum(acc[u]) * ep.inv_hidden + ep.eps);
+                    if (lane == 0) inv_s[t] = inv;
+                }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         }
         if (kNorm && rope) {
-            // this thread's first (token, pair) of the reduction below: its angle does not wait for the product
-            const int npid = (BM / 2) / splits;
+            // this thread's first (token, four pairs) of the reduction below: the token's request, position, cache page
+            // and angles do not wait for the product
+            const int half = ep.rope_head_dim / 2;
+            const int groups = ((BM / 2) / splits) >> 2;
             const int e = (int)threadIdx.x - 64;
             const int tok_n = min(BN, M_tok - tok0);
-            if (e < tok_n * npid) {
-                const int j = e / npid, pid = split * npid + (e - j * npid);
-                const int p = pid % (ep.rope_head_dim / 2);
-                if (p < ep.rope_pairs) sincosf((float)ep.rope_positions[tok0 + j] * ep.rope_inv_freq[p], &rope_sin0, &rope_cos0);
+            if (e < tok_n * groups) {
+                const int j = e / groups, pid = split * (groups << 2) + 4 * (e - j * groups);
+                const int head_local = pid / half, p = pid - head_local * half;
+                const int gh = n0 / ep.rope_head_dim + head_local;
+                rope_req0 = ep.rope_token_req[tok0 + j];
+                rope_pos0 = ep.rope_positions[tok0 + j];
+                if (rope_req0 >= 0) {
+                    if (gh >= ep.rope_nq && ep.rope_write_kv)
+                        rope_page0 = ep.rope_block_table[(size_t)rope_req0 * ep.rope_table_stride + rope_pos0 / ep.rope_page_size];
+                    if (gh < ep.rope_nq + ep.rope_nkv) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (p + c < ep.rope_pairs) sincosf((float)rope_pos0 * ep.rope_inv_freq[p + c], &rope_sin0[c], &rope_cos0[c]);
+                    }
+                }
             }
         }
         const bool ok = mbar_wait_warp(accum_bar, 0);
@@ -308,76 +349,117 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     auto partial = [&](int idx, int s) {
         return splits == 1 ? stage_f32[idx] : ld_cluster_f32(stage_addr + 4u * (uint32_t)idx, (uint32_t)s);
     };
+    // four neighbouring elements (idx a multiple of four)
+    auto partial4 = [&](int idx, int s) {
+        return splits == 1 ? *reinterpret_cast<const float4*>(stage_f32 + idx)
+                           : ld_cluster_f32x4(stage_addr + 4u * (uint32_t)idx, (uint32_t)s);
+    };
+    // The reductions below take four neighbouring features per thread and turn, and ask for everything a turn
+    // needs from global memory before they ask for the partial tiles: a turn costs one round trip, and a tile of
+    // 64 tokens has few turns per thread.
     if (!failed) {
         const int tok_n = min(BN, M_tok - tok0);
         if (kNorm && rope) {
             // Pairs (j, j + head_dim / 2) of a head are rotated together: this block finishes 64 / splits pairs
-            // per token, both members of each.  The four epilogue warps do it (they hold the first angles).
+            // per token, both members of each.  The four epilogue warps do it (they hold what their first turn needs).
             const int D = ep.rope_head_dim, half = D / 2;
-            const int npid = (BM / 2) / splits;
-            const int pid_shift = 31 - __clz(npid);                      // npid is a power of two
-            for (int e = (int)threadIdx.x - 64; e >= 0 && e < tok_n * npid; e += 128) {
-                const int j = e >> pid_shift, pid = split * npid + (e & (npid - 1));
+            const int groups = ((BM / 2) / splits) >> 2;                 // runs of four pairs per token: a power of two
+            const int group_shift = 31 - __clz(groups);
+            for (int e = (int)threadIdx.x - 64; e >= 0 && e < tok_n * groups; e += 128) {
+                const bool first = e == (int)threadIdx.x - 64;
+                const int j = e >> group_shift, pid = split * (groups << 2) + 4 * (e & (groups - 1));
                 const int head_local = pid / half, p = pid - head_local * half;
                 const int lo = head_local * D + p, hi = lo + half;       // features within the tile
                 const int tok = tok0 + j;
-                const int req = ep.rope_token_req[tok];
+                const int req = first ? rope_req0 : ep.rope_token_req[tok];
                 if (req < 0 || n0 + hi >= N_feat) continue;
-                float a[kMaxSplits], b[kMaxSplits];
+                const int pos = first ? rope_pos0 : ep.rope_positions[tok];
+                const int gh = n0 / D + head_local;                     // head among [q | k | v]
+                const bool is_q = gh < ep.rope_nq, rotated = gh < ep.rope_nq + ep.rope_nkv;
+                int page = rope_page0;
+                if (!first && !is_q && ep.rope_write_kv)
+                    page = ep.rope_block_table[(size_t)req * ep.rope_table_stride + pos / ep.rope_page_size];
+                float4 a[kMaxSplits], b[kMaxSplits];
 #pragma unroll
                 for (int s2 = 0; s2 < kMaxSplits; ++s2) {
-                    a[s2] = s2 < splits ? partial(j * BM + lo, s2) : 0.f;
-                    b[s2] = s2 < splits ? partial(j * BM + hi, s2) : 0.f;
+                    a[s2] = s2 < splits ? partial4(j * BM + lo, s2) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    b[s2] = s2 < splits ? partial4(j * BM + hi, s2) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                float x1 = 0.f, x2 = 0.f;
+                float x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int s2 = 0; s2 < kMaxSplits; ++s2) { x1 += a[s2]; x2 += b[s2]; }
-                x1 *= inv_s[j];
-                x2 *= inv_s[j];
-                const int gh = n0 / D + head_local;                     // head among [q | k | v]
-                const int pos = ep.rope_positions[tok];
-                float o1 = x1, o2 = x2;
-                if (gh < ep.rope_nq + ep.rope_nkv && p < ep.rope_pairs) {
-                    float sn = rope_sin0, cs = rope_cos0;
-                    if (e != (int)threadIdx.x - 64) sincosf((float)pos * ep.rope_inv_freq[p], &sn, &cs);
-                    o1 = __fmaf_rn(x1, cs, -__fmul_rn(x2, sn));
-                    o2 = __fmaf_rn(x2, cs, __fmul_rn(x1, sn));
+                for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+                    x1[0] += a[s2].x; x1[1] += a[s2].y; x1[2] += a[s2].z; x1[3] += a[s2].w;
+                    x2[0] += b[s2].x; x2[1] += b[s2].y; x2[2] += b[s2].z; x2[3] += b[s2].w;
                 }
-                if (gh < ep.rope_nq) {
-                    store_out(out + (size_t)tok * ldo + (size_t)gh * D + p, o1);
-                    store_out(out + (size_t)tok * ldo + (size_t)gh * D + p + half, o2);
+                float o1[4], o2[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    x1[c] *= inv_s[j];
+                    x2[c] *= inv_s[j];
+                    o1[c] = x1[c];
+                    o2[c] = x2[c];
+                    if (rotated && p + c < ep.rope_pairs) {
+                        float sn = rope_sin0[c], cs = rope_cos0[c];
+                        if (!first) sincosf((float)pos * ep.rope_inv_freq[p + c], &sn, &cs);
+                        o1[c] = __fmaf_rn(x1[c], cs, -__fmul_rn(x2[c], sn));
+                        o2[c] = __fmaf_rn(x2[c], cs, __fmul_rn(x1[c], sn));
+                    }
+                }
+                const float4 w1 = make_float4(o1[0], o1[1], o1[2], o1[3]), w2 = make_float4(o2[0], o2[1], o2[2], o2[3]);
+                if (is_q) {
+                    OutT* dst = out + (size_t)tok * ldo + (size_t)gh * D + p;
+                    store_out4(dst, w1);
+                    store_out4(dst + half, w2);
                 } else if (ep.rope_write_kv) {
-                    const bool is_v = gh >= ep.rope_nq + ep.rope_nkv;
+                    const bool is_v = !rotated;
                     const int hk = gh - ep.rope_nq - (is_v ? ep.rope_nkv : 0);
-                    const int page = ep.rope_block_table[(size_t)req * ep.rope_table_stride + pos / ep.rope_page_size];
                     __nv_bfloat16* dst = (is_v ? ep.rope_v_cache : ep.rope_k_cache) +
-                        (((size_t)page * ep.rope_nkv + hk) * ep.rope_page_size + pos % ep.rope_page_size) * D;
-                    dst[p] = __float2bfloat16_rn(o1);
-                    dst[p + half] = __float2bfloat16_rn(o2);
+                        (((size_t)page * ep.rope_nkv + hk) * ep.rope_page_size + pos % ep.rope_page_size) * D + p;
+                    store_out4(dst, w1);
+                    store_out4(dst + half, w2);
                 }
             }
         } else if (!gated) {
-            const int slice = BM / splits;             // features this block reduces: a power of two
+            const int slice = BM / splits;             // features this block reduces: a power of two, 16 at least
             const int i0 = split * slice;
-            const int slice_shift = 31 - __clz(slice);
-            for (int e = threadIdx.x; e < tok_n * slice; e += kThreads) {
-                const int j = e >> slice_shift, i = i0 + (e & (slice - 1));
+            const int groups = slice >> 2;             // runs of four features per token
+            const int group_shift = 31 - __clz(groups);
+            for (int e = threadIdx.x; e < tok_n * groups; e += kThreads) {
+                const int j = e >> group_shift, i = i0 + 4 * (e & (groups - 1));
                 if (n0 + i >= N_feat) continue;
-                float v[kMaxSplits];
+                float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
+                float gain[4] = {0.f, 0.f, 0.f, 0.f};
+                const size_t so = (size_t)(tok0 + j) * ep.sink_ld + n0 + i;
+                if (kNorm && sink) {  // a sink's width is whole tiles, its rows are 16-byte aligned (checked by the host)
+                    res = *reinterpret_cast<const float4*>(ep.sink_resid + so);
 #pragma unroll
-                for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? partial(j * BM + i, s) : 0.f;
-                float acc = 0.f;
+                    for (int c = 0; c < 4; ++c) gain[c] = __ldg(ep.sink_gain + n0 + i + c);
+                }
+                float4 v[kMaxSplits];
 #pragma unroll
-                for (int s = 0; s < kMaxSplits; ++s) acc += v[s];
-                if (kNorm) acc *= inv_s[j];
+                for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? partial4(j * BM + i, s) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < kMaxSplits; ++s) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+                if (kNorm) {
+                    const float inv = inv_s[j];
+                    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+                }
                 if (kNorm && sink) {
-                    const size_t o = (size_t)(tok0 + j) * ep.sink_ld + n0 + i;
-                    const float r = ep.sink_resid[o] + acc;
-                    ep.sink_resid[o] = r;
-                    ep.sink_x[o] = __float2bfloat16_rn(r * ep.sink_gain[n0 + i]);
-                    sq_s[j * (BM + 1) + (i - i0)] = r * r;
+                    res.x += acc.x; res.y += acc.y; res.z += acc.z; res.w += acc.w;
+                    *reinterpret_cast<float4*>(ep.sink_resid + so) = res;
+                    store_out4(ep.sink_x + so, make_float4(res.x * gain[0], res.y * gain[1], res.z * gain[2], res.w * gain[3]));
+                    float* sq = sq_s + j * (BM + 1) + (i - i0);
+                    sq[0] = res.x * res.x; sq[1] = res.y * res.y; sq[2] = res.z * res.z; sq[3] = res.w * res.w;
                 } else {
-                    store_out(out + (size_t)(tok0 + j) * ldo + n0 + i, acc);
+                    OutT* dst = out + (size_t)(tok0 + j) * ldo + n0 + i;
+                    if (n0 + i + 3 < N_feat) {
+                        store_out4(dst, acc);
+                    } else {
+                        store_out(dst, acc.x);
+                        if (n0 + i + 1 < N_feat) store_out(dst + 1, acc.y);
+                        if (n0 + i + 2 < N_feat) store_out(dst + 2, acc.z);
+                    }
                 }
             }
             if (kNorm && sink) {
@@ -509,6 +591,8 @@ static int gemm_tc_host(const void* x, const void* w, void* out, int M_tok, int 
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: the norm epilogues take 64 tokens at most, not %d", M_tok);
     if (ep.sink_resid && (N_feat % BM || gated || !ep.sink_gain || !ep.sink_x || !ep.sink_partials))
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink needs %d features to be a multiple of %d, and all its tensors", N_feat, BM);
+    if (ep.sink_resid && (ep.sink_ld % 4 || (uintptr_t)ep.sink_resid % 16))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_gemm_bf16_tc: a sink's residual rows must be 16-byte aligned (row stride %d floats)", ep.sink_ld);
     if (ep.row_partials && ep.n_partials < 1) NS_FAIL(NS_ERR_ARGUMENT, "ns_gemm_bf16_tc: n_partials=%d", ep.n_partials);
     if (ep.rope_positions) {
         const int D = ep.rope_head_dim;

@@ -178,6 +178,16 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local, uint32_t rank) {
     return v;
 }
 
+// four neighbouring floats (a 16-byte aligned address) from the shared memory of block `rank`
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 // a float into the shared memory of block `rank` of this cluster, at the address that `local` has here
 __device__ __forceinline__ void st_cluster_f32(uint32_t local, uint32_t rank, float v) {
     uint32_t remote;

@@ -132,10 +132,10 @@ _tc_state: dict[torch.device, _TensorCoreGemmState] = {}
 _SM_COUNT = 148
 USE_TENSOR_CORE_GEMM = True  # the hand-written tcgen05 kernel; False hands every bf16 product to cuBLAS
 # Products with more tokens than this go to cuBLAS, whose kernels are ahead of the hand-written
-# one there (measured in decode steps of the 8B shape: with 32 tokens the hand-written kernel and its
-# fused epilogues take 3.98 ms against 4.40 ms, with 64 tokens 5.44 ms against 4.9-5.0 ms; at 2,048
-# tokens it reaches 68-85 % of cuBLAS); None = no limit.
-TENSOR_CORE_GEMM_MAX_TOKENS: int | None = 32
+# one there (measured in decode steps of the 8B shape with 1,024 tokens of context: with 32 tokens the
+# hand-written kernel and its fused epilogues take 3.64 ms against 4.40 ms, with 48 tokens 4.71 ms against
+# 4.80 ms, with 64 tokens 4.79 ms against 4.96 ms; at 2,048 tokens it reaches 68-85 % of cuBLAS); None = no limit.
+TENSOR_CORE_GEMM_MAX_TOKENS: int | None = 64
 
 
 def _tc(device: torch.device) -> _TensorCoreGemmState:

@@ -102,8 +102,9 @@ def test_gated_epilogue(M, inter, K, splits):
     torch.testing.assert_close(out3.float(), want.float(), rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("M,H,K,N2", [(1, 128, 64, 256), (8, 4096, 4096, 6144), (16, 256, 520, 384), (5, 384, 14336, 128)])
-def test_norm_epilogues(M, H, K, N2):
+@pytest.mark.parametrize("M,H,K,N2", [(1, 128, 64, 256), (8, 4096, 4096, 6144), (16, 256, 520, 384), (5, 384, 14336, 128),
+                                      (30, 512, 1024, 256), (50, 256, 520, 384), (64, 4096, 4096, 6144)])
+def test_norm_epilogues(M, H, K, N2, monkeypatch):
     """A product that feeds a norm sink (residual sum, gain, partial sums of squares) and the products
     that apply the missing per-row scale, plain and gated - against float64, twice for determinism."""
     from types import SimpleNamespace
@@ -117,6 +118,7 @@ def test_norm_epilogues(M, H, K, N2):
     w2 = (torch.randn(N2, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
     eps = 1e-5
     ws = Workspace(torch.device(DEV))
+    monkeypatch.setattr(o, "TENSOR_CORE_GEMM_MAX_TOKENS", 64)  # the kernel's own limit, whatever the engine's choice of library is
     assert o.norm_fusion_ok(M, torch.bfloat16, w, w2)
     r_want = resid0.double() + x.double() @ w.double().T
     scale = torch.rsqrt((r_want ** 2).mean(dim=1, keepdim=True) + eps)
@@ -145,7 +147,8 @@ def test_norm_epilogues(M, H, K, N2):
         assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("M,nq,nkv,d,K,page", [(1, 4, 2, 64, 256, 8), (8, 32, 8, 128, 4096, 16), (20, 8, 4, 32, 520, 4), (33, 2, 1, 128, 128, 16)])
+@pytest.mark.parametrize("M,nq,nkv,d,K,page", [(1, 4, 2, 64, 256, 8), (8, 32, 8, 128, 4096, 16), (20, 8, 4, 32, 520, 4), (33, 2, 1, 128, 128, 16),
+                                                  (40, 8, 4, 64, 520, 8), (64, 32, 8, 128, 4096, 16)])
 def test_rope_epilogue(M, nq, nkv, d, K, page):
     """The packed projection with rotation and cache write in its epilogue against the projection followed by
     the rotation kernel: the same q, the same pages (a padding row among the tokens is skipped)."""
