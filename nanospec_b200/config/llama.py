@@ -1,7 +1,8 @@
 """Typed configuration of the Llama 3 dense decoder, read from its own config.json keys.
 
 Keys, defaults and refusals follow the reference's `LlamaConfig.from_hf`
-(model/llama.py:22-78): `model_type` must be "llama", biased projections are refused,
+(model/llama.py:22-78): `model_type` must be "llama", biased projections are refused (here also
+an activation other than silu, which the reference would run as silu without a word),
 `rope_parameters` (newer writers) or `rope_theta` + `rope_scaling` (older writers) give
 the rotary constants, only the rope types "default" and "llama3" are known, `head_dim`
 defaults to hidden_size // num_attention_heads, `num_key_value_heads` to the head count,
@@ -103,6 +104,8 @@ class LlamaConfig:
             raise ConfigError(f"not a llama config: model_type={cfg.get('model_type')!r}")
         if cfg.get("attention_bias") or cfg.get("mlp_bias"):
             raise ConfigError("biased projections are not supported")
+        if cfg.get("hidden_act", "silu") != "silu":  # the reference applies silu whatever the key says (model/llama.py:195)
+            raise ConfigError(f"the gated feed-forward applies silu; hidden_act={cfg['hidden_act']!r} is not supported")
         missing = [k for k in _REQUIRED if k not in cfg]
         if missing:
             raise ConfigError(f"config.json lacks required keys: {', '.join(missing)}")

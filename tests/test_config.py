@@ -42,6 +42,7 @@ def test_eos_from_generation_config_wins():
     ({"model_type": "mistral"}, "not a llama config"),
     ({"attention_bias": True}, "biased"),
     ({"mlp_bias": True}, "biased"),
+    ({"hidden_act": "gelu"}, "silu"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "unsupported rope_type"),
     ({"rope_scaling": {"rope_type": "llama3", "factor": 2.0}}, "lacks"),
     ({"num_key_value_heads": 4}, "not a multiple"),
