@@ -7,6 +7,8 @@
     random-weights  write a model folder with seeded random weights from sizes or a config.json
     profile         one decode or prefill step at a named shape, bracketed for a profiler
     replay          trace replay (the same program as bin/trace_run)
+    table           fold the JSON lines of `bench` into a table, the median over the runs of each batch size
+                    (python -m bench.table there, bench/table.py:11-23)
 
 The model folder comes from --model or the NANOSPEC_MODEL environment variable, as in the
 reference (bench/run.py:24).  Token ids go in and come out; there is no tokenizer inside.
@@ -122,6 +124,39 @@ def cmd_bench(args) -> int:
                 "steps": engine.steps, "data": "seeded uniform random token ids"}), flush=True)
             del engine
             torch.cuda.empty_cache()
+    return 0
+
+
+def fold_bench_lines(lines) -> str:
+    """The lines that `bench` printed (anything that does not open with a brace is skipped), folded into a
+    markdown table: one row per (engine, config, batch size) with the medians of its runs."""
+    import statistics
+
+    groups: dict[tuple, list[dict]] = {}
+    for line in lines:
+        line = line.strip()
+        if line.startswith("{"):
+            row = json.loads(line)
+            groups.setdefault((row.get("engine", "?"), row.get("config", "?"), row.get("bs", 0)), []).append(row)
+    out = ["| engine | config | bs | out tok/s | TPOT ms | runs | dtype | gpu |", "|---|---|---|---|---|---|---|---|"]
+    for (engine, config, bs), rows in sorted(groups.items()):
+        def median(key: str):
+            vals = [r[key] for r in rows if r.get(key) is not None]
+            return round(statistics.median(vals), 2) if vals else "-"
+        out.append(f"| {engine} | {config} | {bs} | {median('tok_s')} | {median('tpot_ms')} | {len(rows)} | "
+                   f"{rows[0].get('dtype', '-')} | {rows[0].get('gpu', '-')} |")
+    return "\n".join(out)
+
+
+def cmd_table(args) -> int:
+    lines: list[str] = []
+    for path in args.files or ["-"]:
+        if path == "-":
+            lines.extend(sys.stdin)
+        else:
+            with open(path) as f:
+                lines.extend(f)
+    print(fold_bench_lines(lines))
     return 0
 
 
@@ -374,6 +409,10 @@ def main(argv: list[str] | None = None) -> int:
     r.add_argument("--max-position-embeddings", type=int, default=256)
     r.add_argument("--tie-word-embeddings", action="store_true")
     r.set_defaults(fn=cmd_random_weights)
+
+    tb = sub.add_parser("table", help="fold bench JSON lines (files, or standard input) into a table of medians")
+    tb.add_argument("files", nargs="*", help="files of JSON lines; none or - reads standard input")
+    tb.set_defaults(fn=cmd_table)
 
     p = sub.add_parser("replay", help="trace replay; same options as bin/trace_run", add_help=False)
     p.set_defaults(fn=None)
