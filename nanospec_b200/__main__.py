@@ -287,16 +287,19 @@ def _profile_workload(args, cfg, model) -> int:
         lens = torch.randint(args.prompt_min, args.context + 1, (args.batch,), generator=g).tolist()
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
         args.max_running, args.max_admit = args.batch, 64
-        engine = _engine(model, args, sum(-(-(n + args.new_tokens) // bs) + 1 for n in lens) + 16)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        outs = engine.generate(prompts, SamplingParams(max_tokens=args.new_tokens, ignore_eos=True))
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        runs = []
+        for _ in range(2):  # the second run is the one that counts: the first also loads the library's kernels for these shapes
+            engine = _engine(model, args, sum(-(-(n + args.new_tokens) // bs) + 1 for n in lens) + 16)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            outs = engine.generate(prompts, SamplingParams(max_tokens=args.new_tokens, ignore_eos=True))
+            torch.cuda.synchronize()
+            runs.append(time.perf_counter() - t0)
+        dt = runs[-1]
         new = sum(len(o) for o in outs)
         print(json.dumps({"what": "batch", "shape": args.shape, "requests": args.batch, "prompt_tokens": sum(lens), "new_tokens": new,
-                          "seconds": round(dt, 3), "steps": engine.steps, "new_tokens_per_s": round(new / dt, 1),
-                          "all_tokens_per_s": round((sum(lens) + new) / dt, 1)}), flush=True)
+                          "seconds": round(dt, 3), "first_run_seconds": round(runs[0], 3), "steps": engine.steps,
+                          "new_tokens_per_s": round(new / dt, 1), "all_tokens_per_s": round((sum(lens) + new) / dt, 1)}), flush=True)
         return 0
     dec = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist()
            for n in torch.randint(32, 512, (args.batch,), generator=g)]

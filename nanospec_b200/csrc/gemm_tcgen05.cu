@@ -91,6 +91,9 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+
 __device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
 __device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 // two neighbouring outputs at an address aligned for the pair
@@ -308,20 +311,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else {
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            // 16 or 32 tokens' columns per wait (a lane holds one feature of each)
+            constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
-            for (int c = 0; c < BN / 8; ++c) {
-                if (tok0 + c * 8 >= M_tok) break;  // uniform across the warp
-                uint32_t r[8];
-                tmem_ld8(taddr + c * 8, r);
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                if (tok0 + c0 >= M_tok) break;  // uniform across the warp
+                uint32_t r[CH];
+                tmem_ld_cols(taddr + c0, r);
                 tmem_ld_wait();
                 if (f < N_feat) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int tok = tok0 + c * 8 + j;
+                    for (int j = 0; j < CH; ++j) {
+                        const int tok = tok0 + c0 + j;
                         if (tok < M_tok) {
                             const float v = __uint_as_float(r[j]);
-                            if (splits == 1 && !gated && !sink && !rope) store_out(out + (size_t)tok * ldo + f, kNorm ? v * inv_s[c * 8 + j] : v);
-                            else stage_f32[(c * 8 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
+                            if (splits == 1 && !gated && !sink && !rope) store_out(out + (size_t)tok * ldo + f, kNorm ? v * inv_s[c0 + j] : v);
+                            else stage_f32[(c0 + j) * BM + q * 32 + lane] = v;  // this block's partial tile, [token][feature]
                         }
                     }
                 }
