@@ -59,9 +59,13 @@ def build_model(cfg_json: dict, generation_json: dict | None, dtype: torch.dtype
     return model, config
 
 
-def load_model(folder: str | Path, device: str | torch.device = "cuda", dtype: torch.dtype = torch.bfloat16) -> DecoderModel:
-    """Counterpart of the reference's `load_model(model, device, dtype)` (model/loader.py:41-83)
-    for a local folder."""
+def load_model(folder: str | Path, device: str | torch.device = "cuda", dtype: torch.dtype = torch.bfloat16,
+               backend: str = "auto") -> DecoderModel:
+    """Counterpart of the reference's `load_model(model, device, dtype, backend)` (model/loader.py:41-83)
+    for a local folder.  `backend` is taken so that a call written for the reference still reads; there
+    is one execution path here (this package's CUDA kernels), so anything but "auto" is refused."""
+    if backend != "auto":
+        raise ValueError(f"backend={backend!r}: this engine has one execution path, its own CUDA kernels; pass \"auto\"")
     folder = Path(folder)
     cfg_json, gen_json = read_config_files(folder)
     model, _ = build_model(cfg_json, gen_json, dtype, device)

@@ -56,8 +56,10 @@ def test_random_folder_is_reproducible_and_loads(tiny_folders, tmp_path):
         assert abs(float(gains.mean()) - 1.0) < 0.1 and 0.03 < float(gains.std()) < 0.2
         w = f.tensor("model.layers.0.mlp.up_proj.weight").float()
         assert abs(float(w.std()) - 0.02) < 0.004
-    b = load_model(tiny_folders["B"], device="cpu", dtype=torch.float32)
+    b = load_model(tiny_folders["B"], device="cpu", dtype=torch.float32, backend="auto")  # the reference's fourth argument
     assert b.head.weight is not b.embedding.table and b.head.weight.dtype == torch.float32
+    with pytest.raises(ValueError, match="one execution path"):
+        load_model(tiny_folders["B"], device="cpu", backend="sdpa")
 
 
 def _resave(folder, out, change):
