@@ -46,6 +46,10 @@ class Engine:
         self._score_bufs: list = [None, None]
         self._score_turn = 0
         self.launched_ahead = 0  # steps that were launched before their predecessor had been read
+        # set to a list to have every launched step noted as (tokens, cache positions its requests hold after it,
+        # rows sampled, query-key pairs under the causal mask): what a measurement needs to set a workload's time
+        # against its flops and bytes
+        self.step_log: list[tuple[int, int, int, int]] | None = None
         self.d2h_bytes_last = 0
 
     # ---- profiling (CUDA events per phase, read once per step) -------------------------------
@@ -124,6 +128,10 @@ class Engine:
     def _launch(self, batch: list[Scheduled], prev):
         """Launches the step and returns a handle to collect it with.  `prev`: the step in flight whose
         sampled tokens this one takes on the device (entries with `from_row`), or None."""
+        if self.step_log is not None:
+            self.step_log.append((sum(len(s.tokens) for s in batch), sum(s.req.committed + len(s.tokens) for s in batch),
+                                  sum(1 for s in batch if s.samples),
+                                  sum(len(s.tokens) * (2 * s.req.committed + len(s.tokens) + 1) // 2 for s in batch)))
         if self.graphs is not None and self.graphs.can_run(batch):
             take = None if prev is None else (prev.tok_dev, [s.from_row for s in batch])
             flight = self.graphs.launch(batch, self._uniforms(batch), take)
