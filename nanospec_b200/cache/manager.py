@@ -64,6 +64,12 @@ class CacheManager:
     def state_slot(self, req_id: int) -> int:
         return self.slots.owner[req_id]
 
+    @property
+    def scratch_slot(self) -> int:
+        """The state slot that no request ever holds: padding rows of a step carry it, so that a mixer
+        which reads and writes state by `state_slot` on the device needs no mask for them."""
+        return self.slots.num_slots
+
     # ---- life of a request ----------------------------------------------------------------
     def begin(self, req_id: int) -> None:
         if req_id in self.seq_len:

@@ -27,7 +27,8 @@ class CacheStorage:
         self.state: dict[int, torch.Tensor] = {}
         for lane, (_, st) in enumerate(lane_needs):
             if st is not None:
-                self.state[lane] = torch.zeros((manager.slots.num_slots, *st.shape), dtype=st.dtype, device=device)
+                # one slot more than requests can hold: the scratch slot that a step's padding rows point at
+                self.state[lane] = torch.zeros((manager.slots.num_slots + 1, *st.shape), dtype=st.dtype, device=device)
         self.lane_needs = lane_needs
 
     def bytes(self) -> int:

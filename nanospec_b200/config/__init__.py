@@ -1,4 +1,5 @@
-from .llama import ConfigError, Llama3RopeScaling, LlamaConfig, read_config_files
+from .files import ConfigError, read_config_files
+from .llama import Llama3RopeScaling, LlamaConfig
 from .recipe import LayerSpec, ModelRecipe, PartSpec, Run
 from .registry import Architecture, register_architecture, registered_architectures, resolve_architecture
 from .engine import EngineConfig

@@ -11,14 +11,10 @@ defaults to hidden_size // num_attention_heads, `num_key_value_heads` to the hea
 
 from __future__ import annotations
 
-import json
 from dataclasses import dataclass, field
-from pathlib import Path
 from typing import Any
 
-
-class ConfigError(ValueError):
-    """A config.json that this framework cannot run, with the reason."""
+from .files import ConfigError
 
 
 @dataclass(frozen=True)
@@ -181,15 +177,3 @@ class LlamaConfig:
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return out
-
-
-def read_config_files(folder: str | Path) -> tuple[dict[str, Any], dict[str, Any] | None]:
-    """config.json and, when present, generation_config.json of a model folder."""
-    folder = Path(folder)
-    path = folder / "config.json"
-    if not path.is_file():
-        raise ConfigError(f"no config.json in {folder}")
-    cfg = json.loads(path.read_text())
-    gen_path = folder / "generation_config.json"
-    gen = json.loads(gen_path.read_text()) if gen_path.is_file() else None
-    return cfg, gen

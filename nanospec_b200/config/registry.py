@@ -11,7 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .llama import ConfigError
+from .files import ConfigError
 from .recipe import ModelRecipe
 
 

@@ -369,8 +369,21 @@ NS_API int ns_attention_decode_noalloc(const void* q, int q_stride, const void* 
                                        const int* rows, int n_tokens, int nq, int nkv, int head_dim, int page_size,
                                        float scale, int window, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
-    if (nkv < 1 || nq < nkv || nq % nkv || n_splits < 1 || head_dim < 1)
-        NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode_noalloc: nq=%d nkv=%d head_dim=%d n_splits=%d", nq, nkv, head_dim, n_splits);
+    // every refusal comes before anything is put on the stream
+    if (head_dim % 16 || head_dim < 16 || head_dim > 128)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_noalloc: head_dim=%d (multiples of 16 up to 128)", head_dim);
+    if (nkv < 1 || nq < nkv || nq % nkv)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_noalloc: %d query heads over %d kv heads", nq, nkv);
+    if (n_splits < 1 || n_splits > kMaxSplits)
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode_noalloc: n_splits=%d (1..%d)", n_splits, kMaxSplits);
+    if (q_stride % 8 || ((uintptr_t)q % 16))
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_noalloc: q rows must be 16-byte aligned");
+    if (n_tokens > 65535)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_noalloc: %d tokens exceed the grid's z extent", n_tokens);
+    if (n_splits == 1)  // one block sees all of a request's keys: no partial results, no counters, no scratch
+        return ns_attention_decode(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr,
+                                   out, o_stride, nullptr, nullptr, nullptr, rows, n_tokens, nq, nkv, head_dim, page_size,
+                                   scale, window, 1, stream);
     long long o_floats, ml_floats, ctr_ints;
     ns_attention_decode_scratch(n_tokens, nq, nkv, head_dim, n_splits, &o_floats, &ml_floats, &ctr_ints);
     const size_t ctr_bytes = round256((size_t)ctr_ints * sizeof(int));

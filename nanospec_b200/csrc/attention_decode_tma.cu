@@ -96,8 +96,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int n = rows ? rows[z] : z;  // the token this cluster works for
     const int hk = blockIdx.y / head_tiles, ht = blockIdx.y - hk * head_tiles;
     const int req = token_req[n];
-    if (req < 0) return;                                        // the same for every block of the cluster
-    if (qo_indptr[req + 1] - qo_indptr[req] != 1) return;
+    // (the same for every block of the cluster; a block with nothing to do still waits for the predecessor, so that
+    // a grid of nothing but such blocks cannot complete before it and let its own successor start too early)
+    if (req < 0 || qo_indptr[req + 1] - qo_indptr[req] != 1) { ns_pdl_wait(); return; }
     // a block's shared memory may be written by the others only once it runs: every block says so here
     // and checks the others before its first store into them
     if (n_splits > 1) cluster_arrive();

@@ -117,6 +117,9 @@ __device__ __forceinline__ float ns_block_max(float v, float* scratch) {
 // ns_pdl_wait() before it touches anything the predecessor wrote (or writes anything the
 // predecessor may read).  What runs before that wait - barrier set-up, TMEM allocation, the first
 // weight tiles of a matrix product - overlaps the predecessor.  ns_set_pdl(0) turns this off.
+// Every block waits before it returns, also one that has nothing to do (a padding row): a grid none of
+// whose blocks waited would complete while its predecessor still runs, and the wait of ITS successor,
+// which covers the grid directly before it only, would no longer mean "everything earlier is done".
 extern int ns_pdl_enabled;
 
 __device__ __forceinline__ void ns_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

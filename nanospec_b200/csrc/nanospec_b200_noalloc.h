@@ -19,7 +19,9 @@
  *    (ns_last_error()) that states the bytes needed and the limit.  The need is
  *        4 * n_tokens * nq * n_splits * (head_dim + 2)  bytes for the partial results
  *      + 4 * n_tokens * nkv * ceil((nq / nkv) / 16)     bytes for the arrival counters,
- *    each part rounded up to 256 bytes.
+ *    each part rounded up to 256 bytes.  With n_splits == 1 nothing is shared between blocks, the array is
+ *    not touched and no size is refused.  Arguments that ns_attention_decode() would refuse are refused here
+ *    before anything is put on the stream.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) with
  *    that device current.  Make that first call at start-up, before any stream capture begins.
  *  - All calls on a device share the one array and it keeps the previous call's contents.  The

@@ -24,9 +24,11 @@ rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, con
     // are read and computed before this kernel waits for it; only the projection itself comes after.
     const int n = blockIdx.x, hh = blockIdx.y;
     const int req = token_req[n];
-    if (req < 0) return;
+    // a block with nothing to do still waits: a grid whose blocks all left early would complete while its
+    // predecessor runs, and its successor's wait would then cover this grid only
+    if (req < 0) { ns_pdl_wait(); return; }
     const bool is_q = hh < nq, is_v = hh >= nq + nkv;
-    if (!is_q && !write_kv) return;
+    if (!is_q && !write_kv) { ns_pdl_wait(); return; }
     const int pos = positions[n];
     const int half = d / 2;
     T* x = qkv + (size_t)n * (nq + 2 * nkv) * d + (size_t)hh * d;
@@ -72,7 +74,7 @@ rope_kv_write_token_kernel(T* __restrict__ qkv, const int* __restrict__ position
     extern __shared__ float cs[];  // [rot_pairs] cos, then [rot_pairs] sin
     const int n = blockIdx.x;
     const int req = token_req[n];
-    if (req < 0) return;
+    if (req < 0) { ns_pdl_wait(); return; }  // (see rope_kv_write_kernel)
     const int pos = positions[n];
     const int half = d / 2;
     for (int j = threadIdx.x; j < rot_pairs; j += blockDim.x) {

@@ -121,7 +121,7 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     __shared__ int iscratch[32];
     __shared__ float seg_prefix[kThreads];
     __shared__ int seg_eq_prefix[kThreads];
-    __shared__ int found;
+    __shared__ int found, last_kept;
     __shared__ float smax[32];
     __shared__ int sidx[32];
 
@@ -270,7 +270,7 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
         }
     }
     seg_prefix[tid] = segsum;
-    if (tid == 0) found = 0x7fffffff;
+    if (tid == 0) { found = 0x7fffffff; last_kept = 0; }
     __syncthreads();
     if (warp == 0) {
         // 32 consecutive segments per lane, then a warp scan of the lane totals
@@ -293,22 +293,28 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     const float total = fscratch[0];
     const float target = u[row] * total;
     {
+        // the running sum is compared with the target only right after a kept token has been added: a token
+        // outside the set can never be reported, whatever the rounding of the scanned prefix
         float run = seg_prefix[tid];
-        int eq_seen = 0;
+        int eq_seen = 0, last = -1;
         for (int i = s0; i < s1; ++i) {
             const float v = z[i] / temp;
-            if (kept(i, v, eq_seen)) run += expf(v - lse_s);
-            if (run > target) { atomicMin(&found, i); break; }
+            if (kept(i, v, eq_seen)) {
+                run += expf(v - lse_s);
+                last = i;
+                if (run > target) { atomicMin(&found, i); break; }
+            }
         }
+        if (last >= 0) atomicMax(&last_kept, last);  // used only if no thread's sum passed the target
     }
     __syncthreads();
     if (tid == 0) {
         int t = found;
-        if (t > vocab - 1) t = vocab - 1;
+        if (t > vocab - 1) t = last_kept;  // rounding left the target at or past the total: the last token of the set
         token[row] = t;
         logprob_raw[row] = z[t] - lse_raw;
         const float v = z[t] / temp;
-        // a clamped draw can land on a token outside the nucleus; its processed log-prob is -inf
+        // (an empty set cannot occur: the largest logit is always kept)
         bool in_set = true;
         if (nucleus) {
             const unsigned key = order_key(v);

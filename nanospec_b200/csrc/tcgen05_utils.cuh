@@ -38,15 +38,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // bounded wait: false when the limit ran out (the caller records the error and winds down).
-// The limit is kWaitLimitNs of wall time, checked every 1024 polls, and kSpinLimit polls at most.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// The limit is `limit_ns` of wall time (kWaitLimitNs unless given), looked at every `check_mask` + 1 polls
+// (1024 unless given), and kSpinLimit polls at most.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs,
+                                          uint32_t check_mask = 1023u) {
     unsigned long long t0 = 0;
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u) {
+        if ((i & check_mask) == check_mask) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
+            else if (now - t0 > limit_ns) return false;
         }
     }
     return false;

@@ -30,8 +30,11 @@ def _pad4(n: int) -> int:
 class _Bucket:
     """Static buffers and the captured graph of one batch size."""
 
-    def __init__(self, runner: ModelRunner, size: int, table_width: int, workspace: Workspace, pool) -> None:
+    def __init__(self, runner: ModelRunner, size: int, table_width: int, pool) -> None:
         self.size, self.width = size, table_width
+        self.scratch_slot = runner.manager.scratch_slot  # where padding rows keep their (meaningless) state
+        # scratch of this bucket alone: the graph holds pointers into it, so nothing else may ever make it grow
+        workspace = self.workspace = Workspace(runner.device)
         m = runner.manager
         n_groups = len(m.groups)
         names = ["positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
@@ -94,11 +97,12 @@ class _Bucket:
 
     def _fill_padding(self, first: int) -> None:
         o, n = self.off, self.size
+        scratch_slot = self.scratch_slot
         self.ids_host[first:] = -1
         self.host_np[o["token_req"] + first: o["token_req"] + n] = -1
         self.host_np[o["positions"] + first: o["positions"] + n] = 0
         self.host_np[o["kv_len"] + first: o["kv_len"] + n] = 0
-        self.host_np[o["slots"] + first: o["slots"] + n] = 0
+        self.host_np[o["slots"] + first: o["slots"] + n] = scratch_slot
         self.host_np[o["top_k"] + first: o["top_k"] + n] = 0
         self.host_f32[o["temperature"] + first: o["temperature"] + n] = 0.0
         self.host_f32[o["top_p"] + first: o["top_p"] + n] = 1.0
@@ -128,6 +132,7 @@ class _Bucket:
             self._forward(runner)
         self.kernels = lib.launch_count() - before  # this framework's kernels in one replay
         self.graph = g
+        self.workspace.frozen = True  # a buffer that would have to move now raises instead
 
 
 class DecodeGraphs:
@@ -137,7 +142,6 @@ class DecodeGraphs:
         self.sizes = tuple(sorted(buckets))
         max_context = min(runner.max_positions, runner.manager.num_blocks * runner.block_size)
         self.table_width = max(1, -(-max_context // runner.block_size))
-        self.workspace = Workspace(runner.device)  # the graphs' own scratch: never grows after capture
         self.pool = torch.cuda.graph_pool_handle()
         self.buckets: dict[int, _Bucket] = {}
         self.replays = 0
@@ -158,7 +162,7 @@ class DecodeGraphs:
 
     def _bucket(self, size: int) -> _Bucket:
         if size not in self.buckets:
-            self.buckets[size] = _Bucket(self.runner, size, self.table_width, self.workspace, self.pool)
+            self.buckets[size] = _Bucket(self.runner, size, self.table_width, self.pool)
         return self.buckets[size]
 
     def run(self, batch: list[Scheduled], uniforms: list[float]):

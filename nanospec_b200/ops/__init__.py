@@ -129,7 +129,19 @@ class _TensorCoreGemmState:
 
 
 _tc_state: dict[torch.device, _TensorCoreGemmState] = {}
-_SM_COUNT = 148
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (148 on a B200): the one place the launch heuristics
+    below take the size of the chip from."""
+    dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return n
+
+
 USE_TENSOR_CORE_GEMM = True  # the hand-written tcgen05 kernel; False hands every bf16 product to cuBLAS
 # Products with more tokens than this go to cuBLAS, whose kernels are ahead of the hand-written
 # one there (measured in decode steps of the 8B shape with 1,024 tokens of context: with 32 tokens the
@@ -162,8 +174,20 @@ def check_kernel_errors(device: torch.device | None = None) -> None:
                     3: "matrix product: the epilogue waited for the accumulator", 4: "matrix product: copies in flight did not land",
                     11: "prefill attention: the loader waited for a free stage", 12: "prefill attention: the MMA issuer waited",
                     13: "prefill attention: a softmax warp waited", 21: "decode attention: the loader waited for a free stage",
-                    22: "decode attention: a warp waited for its keys"}.get(code, "?")
-            raise KernelError(f"a kernel gave up after waiting two seconds on an mbarrier - {what} (code {code}); its output is not valid")
+                    22: "decode attention: a warp waited for its keys",
+                    31: "wait probe: nobody arrives at its barrier"}.get(code, "?")
+            raise KernelError(f"a kernel gave up waiting on an mbarrier (the limit is two seconds) - {what} (code {code}); "
+                              "its output is not valid")
+
+
+def wait_probe(device: torch.device, limit_ns: int = 1_000_000) -> bool:
+    """Launches the one-block kernel of csrc/wait_probe.cu, whose only thread waits `limit_ns` on a barrier at
+    which nobody arrives, gives up and records its code in the device's error word, as the production kernels'
+    bounded waits do.  Returns whether the wait completed (it cannot); `check_kernel_errors` raises afterwards."""
+    st = _tc(torch.device(device) if not isinstance(device, torch.device) else device)
+    ok = torch.full((1,), -1, dtype=torch.int32, device=st.device)
+    lib.call("ns_wait_probe", st.error.data_ptr(), int(limit_ns), ok.data_ptr(), _stream())
+    return bool(ok.item() == 1)
 
 
 def gemm_splits(M: int, N: int, K: int) -> int:
@@ -172,7 +196,7 @@ def gemm_splits(M: int, N: int, K: int) -> int:
     tokens_per_block = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // tokens_per_block)
     k_blocks = -(-K // 64)
-    resident = _SM_COUNT * (2 if tokens_per_block <= 64 else 1)
+    resident = sm_count() * (2 if tokens_per_block <= 64 else 1)
     want = max(1, min(8, resident // tiles, k_blocks // 8))
     return 1 << (want.bit_length() - 1)  # the blocks of a tile form a cluster of 1, 2, 4 or 8
 
@@ -460,7 +484,11 @@ def kv_store(qkv: torch.Tensor, ctx, lane, nq: int, nkv: int, head_dim: int) -> 
 TILE_Q = 128         # query rows per block of the m16n8k16 prefill kernel
 TILE_Q_TCGEN05 = 256 # and of the tcgen05 one (two tiles of 128)
 USE_TCGEN05_ATTENTION = True
-_TARGET_BLOCKS = 296  # decode attention wants about two blocks per SM of a B200 before it splits keys further
+
+
+def _target_blocks() -> int:
+    """Decode attention wants about two blocks per SM before it splits keys further."""
+    return 2 * sm_count()
 
 
 def _tensor_core_attention(dtype: torch.dtype, head_dim: int) -> bool:
@@ -475,7 +503,7 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
     within two blocks per SM (measured on a B200: 16 at one request, 4 at 8, 1 at 64, for contexts of
     1,024 and 4,096), and, when the longest context is known, at least two tiles of 64 keys per block."""
     n_splits = 1
-    while n_splits < 16 and blocks * n_splits * 2 <= _TARGET_BLOCKS:
+    while n_splits < 16 and blocks * n_splits * 2 <= _target_blocks():
         n_splits *= 2
     if max_kv_len is not None:
         while n_splits > 1 and max_kv_len < 128 * n_splits:
@@ -499,7 +527,7 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
                  nkv, head_dim, lane.page_size, float(scale), int(window), n_splits, _tc(qkv.device).error.data_ptr(),
                  _stream())
         return
-    n_splits = max(1, min(16, -(-_TARGET_BLOCKS // (n_rows * nkv * head_tiles))))
+    n_splits = max(1, min(16, -(-_target_blocks() // (n_rows * nkv * head_tiles))))
     if max_kv_len is not None:
         # long contexts split further (measured: 4 splits are best at 4,096 keys even for 64 requests),
         # and a split keeps at least two tiles of keys

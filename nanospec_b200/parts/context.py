@@ -58,6 +58,15 @@ class StepContext:
     tables; negative = padding row, skipped by every kernel) and sits at `positions[n]` of
     its sequence.  Request b's tokens are rows qo_indptr[b] .. qo_indptr[b+1] and after this
     step it holds kv_len[b] positions.  `state_slot[b]` is its slot of fixed-size state.
+
+    What a mixer with state may rely on.  `lane.state` is [slots + 1, *shape]; request b's state is
+    `lane.state[state_slot[b]]`, zero when the request brings its first tokens, and the mixer leaves in it
+    the state after the request's last token of this step.  In a decode step replayed from a CUDA graph
+    only the device tensors are current: `q_lens`, `kv_lens` and `state_slots_host` are fixed at capture
+    (every request brings one token) and `state_slots_host` is empty, so a mixer that wants to run under
+    graphs addresses its state through `state_slot`, `token_req` and `qo_indptr` on the device.  Padding
+    rows (token_req < 0) carry the scratch slot, the last one, which no request holds: they may be read
+    and written like any other and need no mask.
     """
 
     n_tokens: int

@@ -16,7 +16,7 @@ from pathlib import Path
 
 import torch
 
-from ..config.llama import read_config_files
+from ..config.files import read_config_files
 from ..config.registry import resolve_architecture
 from ..parts.base import WeightSpec
 from ..parts.model import DecoderModel

@@ -68,6 +68,32 @@ def tiny_folders(tmp_path_factory) -> dict[str, Path]:
     return out
 
 
+# Two-layer models at real layer widths, which select the kernels that the tiny ones never reach (TMA decode
+# attention in a cluster, tcgen05 prefill attention, the products' gated, norm and rotation epilogues):
+# "wide128" has the benchmark configuration's widths, "wide64" those of its smallest sibling with heads of 64 and
+# a tied head.  Vocabularies are no power of two.
+WIDE = {
+    "wide128": LlamaConfig(vocab_size=20011, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
+                           num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+                           max_position_embeddings=1024, rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 256),
+                           tie_word_embeddings=True),
+    "wide64": LlamaConfig(vocab_size=10007, hidden_size=2048, intermediate_size=8192, num_hidden_layers=2,
+                          num_attention_heads=32, num_key_value_heads=8, head_dim=64, rms_norm_eps=1e-5, rope_theta=500000.0,
+                          max_position_embeddings=1024, rope_scaling=Llama3RopeScaling(32.0, 1.0, 4.0, 256),
+                          tie_word_embeddings=True),
+}
+
+
+@pytest.fixture(scope="session")
+def wide_folders(tmp_path_factory) -> dict[str, Path]:
+    out = {}
+    for i, (name, cfg) in enumerate(WIDE.items()):
+        d = tmp_path_factory.mktemp(name)
+        write_random_model(d, cfg, seed=21 + i)
+        out[name] = d
+    return out
+
+
 def random_ids(n: int, vocab: int, seed: int) -> list[int]:
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()

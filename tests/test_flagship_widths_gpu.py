@@ -19,16 +19,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(scope="module")
-def folder(tmp_path_factory):
-    from nanospec_b200.config import Llama3RopeScaling, LlamaConfig
-    from nanospec_b200.weights import write_random_model
-    cfg = LlamaConfig(vocab_size=20011, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
-                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
-                      max_position_embeddings=1024, rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 256),
-                      tie_word_embeddings=True)
-    d = tmp_path_factory.mktemp("flagship_widths")
-    write_random_model(d, cfg, seed=21)
-    return d
+def folder(wide_folders):
+    return wide_folders["wide128"]
 
 
 @pytest.fixture(scope="module")

@@ -5,8 +5,10 @@ Its scratch is a fixed 8 MiB array inside the library instead of caller-provided
 
 The test calls the entry point through its exported C symbol, twice in a row with different
 problems on the shared array, and compares each result with ns_attention_decode given
-freshly allocated scratch; then checks that a problem too large for the array is refused with
-a message that names the limit.  The file sorts last so that a run that stops at the first
+freshly allocated scratch and with a plain softmax over the keys and values gathered from the
+pages (the cache laid out as the kernels read it: [page, kv head, offset, dim]); then checks
+that a problem too large for the array is refused with a message that names the limit, and
+that one split, which needs no scratch, is never refused for its size.  The file sorts last so that a run that stops at the first
 failure has already run every other test."""
 
 from __future__ import annotations
@@ -38,8 +40,8 @@ def _lib():
 def _problem(n_req, S, nq, nkv, d, page, seed):
     g = torch.Generator().manual_seed(seed)
     n_pages = n_req * (-(-S // page)) + 5
-    kc = (torch.randn(n_pages, page, nkv, d, generator=g)).to(torch.bfloat16).to(DEV)
-    vc = (torch.randn(n_pages, page, nkv, d, generator=g)).to(torch.bfloat16).to(DEV)
+    kc = (torch.randn(n_pages, nkv, page, d, generator=g)).to(torch.bfloat16).to(DEV)  # [page, kv head, offset, dim]
+    vc = (torch.randn(n_pages, nkv, page, d, generator=g)).to(torch.bfloat16).to(DEV)
     perm = torch.randperm(n_pages, generator=g)
     width = -(-S // page)
     tables = perm[: n_req * width].view(n_req, width).to(torch.int32).to(DEV)
@@ -47,7 +49,22 @@ def _problem(n_req, S, nq, nkv, d, page, seed):
     q = torch.randn(n_req, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16).to(DEV)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     return dict(q=q, kc=kc, vc=vc, tables=tables, token_req=i32(list(range(n_req))), positions=i32([n - 1 for n in lens]),
-                qo=i32(list(range(n_req + 1))), n=n_req, nq=nq, nkv=nkv, d=d, page=page)
+                qo=i32(list(range(n_req + 1))), n=n_req, nq=nq, nkv=nkv, d=d, page=page, lens=lens)
+
+
+def _plain(p):
+    """softmax(q k^T / sqrt(d)) v per request over the keys gathered from its pages, in float32."""
+    import plain_llama as plain
+    nq, nkv, d = p["nq"], p["nkv"], p["d"]
+    out = []
+    for r, n in enumerate(p["lens"]):
+        pages = p["tables"][r].long()
+        k = p["kc"][pages].permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n].float()   # [keys, kv head, dim]
+        v = p["vc"][pages].permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n].float()
+        q = torch.zeros(n, nq, d, device=DEV)
+        q[-1] = p["q"][r, : nq * d].float().view(nq, d)                            # the one query sits at the last position
+        out.append(plain.plain_attention(q, k, v)[-1].reshape(-1))
+    return torch.stack(out)
 
 
 def _run(lib, p, n_splits, no_alloc):
@@ -81,6 +98,7 @@ def test_no_alloc_entry_point_matches_the_allocating_one_on_two_calls_in_a_row()
         assert torch.isfinite(got.float()).all()
         torch.testing.assert_close(got.float(), want.float(), rtol=3e-2, atol=3e-2)
         assert torch.equal(got, want)  # same kernel, same order of sums: the same bits
+        torch.testing.assert_close(got.float(), _plain(p), rtol=2e-2, atol=2e-2)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
@@ -96,3 +114,12 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     assert rc == 0, lib.ns_last_error().decode()
     rc, want = _run(lib, p, 2, no_alloc=False)
     assert torch.equal(got, want)
+    torch.testing.assert_close(got.float(), _plain(p), rtol=2e-2, atol=2e-2)
+    # one split shares nothing between blocks: no scratch, so no size is too large
+    big = _problem(n_req=600, S=40, nq=32, nkv=8, d=128, page=16, seed=4)
+    rc, got = _run(lib, big, 1, no_alloc=True)
+    assert rc == 0, lib.ns_last_error().decode()
+    torch.testing.assert_close(got.float(), _plain(big), rtol=2e-2, atol=2e-2)
+    # and what the kernel refuses is refused before anything reaches the stream
+    rc, _ = _run(lib, p, 17, no_alloc=True)
+    assert rc != 0 and "n_splits" in lib.ns_last_error().decode()

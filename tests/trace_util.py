@@ -158,3 +158,33 @@ def peak_tokens(steps: list[dict], round_to: int = 64) -> int:
         for name in rec["end"]:
             held.pop(name, None)
     return peak
+
+
+def replay_in_process(model, steps: list[dict], num_blocks: int, block_size: int, max_requests: int = 8):
+    """Drives the framework's `ModelRunner` (what bin/trace_run drives) inside this process, so that a test can
+    look at the cache manager meanwhile.  Returns ({step: float32 [wanted, vocab]}, {request: set of pages it
+    ever held}, the runner)."""
+    from nanospec_b200.engine import ModelRunner, StepEntry
+
+    runner = ModelRunner(model, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests)
+    ids: dict[str, int] = {}
+    pages: dict[str, set[int]] = {}
+    results = {}
+    for rec in steps:
+        entries = []
+        for e in rec["entries"]:
+            if e["id"] not in ids:
+                ids[e["id"]] = len(pages)
+                pages[e["id"]] = set()
+                runner.begin(ids[e["id"]])
+            entries.append(StepEntry(ids[e["id"]], e["tokens"], e.get("want", [])))
+        out = runner.step(entries)
+        if out is not None:
+            results[rec["step"]] = out.float().cpu().numpy()
+        for e in rec["entries"]:
+            for gi in range(len(runner.manager.groups)):
+                pages[e["id"]].update(p for p in runner.manager.table(gi, ids[e["id"]]) if p >= 0)
+        for name in rec["end"]:
+            runner.end(ids.pop(name))
+        runner.manager.check()
+    return results, pages, runner
