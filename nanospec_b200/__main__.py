@@ -314,14 +314,20 @@ def _profile_workload(args, cfg, model) -> int:
     lreqs = [engine.add(p, SamplingParams(max_tokens=2, temperature=1.0, seed=99 + i, ignore_eos=True)) for i, p in enumerate(longs)]
     torch.cuda.synchronize()
     t0, s0 = time.perf_counter(), engine.steps
+    h0 = (engine.host_compose_s, engine.host_launch_s)
     while any(r.state != "done" for r in lreqs):
+        if args.sync_steps:
+            torch.cuda.synchronize()  # an empty launch queue: the host timers then hold the host's own work only
         engine.step()
     torch.cuda.synchronize()
     dt, steps = time.perf_counter() - t0, engine.steps - s0
+    host = (engine.host_compose_s - h0[0], engine.host_launch_s - h0[1])
     print(json.dumps({"what": "mixed", "shape": args.shape, "decoding_requests": args.batch, "long_prompts": args.long,
                       "prompt_tokens_each": args.context, "portion": args.prefill_chunk, "seconds": round(dt, 3), "steps": steps,
                       "ms_per_step": round(1000 * dt / steps, 3), "prefill_tokens_per_s": round(args.long * args.context / dt, 1),
-                      "decoded_meanwhile": steps * args.batch}), flush=True)
+                      "decoded_meanwhile": steps * args.batch, "launched_ahead": engine.launched_ahead,
+                      "host_compose_ms_per_step": round(1000 * host[0] / steps, 3),
+                      "host_launch_ms_per_step": round(1000 * host[1] / steps, 3)}), flush=True)
     return 0
 
 
@@ -392,6 +398,9 @@ def main(argv: list[str] | None = None) -> int:
                     help="queue: requests in all (default 3 x --batch), through --batch live slots; prompts of --prompt-min to "
                          "--context tokens, --new-tokens / 4 to --new-tokens new ones")
     pr.add_argument("--steps", type=int, default=1, help="decode steps to time (the median is printed)")
+    pr.add_argument("--sync-steps", action="store_true",
+                    help="mixed: wait for the GPU before every step, so that host_compose_ms and host_launch_ms hold the "
+                         "host's own work and no waiting for room in the launch queue (use with --no-lookahead)")
     pr.set_defaults(fn=cmd_profile)
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")

@@ -1,5 +1,5 @@
-from .manager import CacheManager
-from .pages import RELEASED, CacheGroup, GroupSpec, PagePool, PoolExhausted, SlotPool
+from .manager import CacheGroup, CacheManager
+from .pages import RELEASED, GroupSpec, PoolExhausted
 from .storage import CacheStorage
 
-__all__ = ["CacheGroup", "CacheManager", "CacheStorage", "GroupSpec", "PagePool", "PoolExhausted", "RELEASED", "SlotPool"]
+__all__ = ["CacheGroup", "CacheManager", "CacheStorage", "GroupSpec", "PoolExhausted", "RELEASED"]

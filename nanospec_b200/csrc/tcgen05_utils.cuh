@@ -5,6 +5,8 @@
 
 #include <cuda.h>
 
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace {
@@ -221,9 +223,37 @@ inline NsEncodeTiledFn ns_encode_fn() {
 }
 
 // rows x cols bf16 matrix with row stride ld (elements); boxes of box_rows x 64 columns, 128-byte
-// swizzle, zero fill outside the matrix
+// swizzle, zero fill outside the matrix.  A map depends on the address, the sizes and the box only, never on the
+// contents, and weights and scratch buffers keep their addresses from step to step: every map is encoded once and
+// kept (per host thread and per source file that asks; the table is emptied when it reaches 8,192 entries), so
+// that an eager step does not encode some hundred maps again.
+struct NsMapKey {
+    const void* ptr;
+    unsigned long long rows;
+    long long ld;
+    int cols, box_rows;
+    bool operator==(const NsMapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && ld == o.ld && cols == o.cols && box_rows == o.box_rows;
+    }
+};
+struct NsMapKeyHash {
+    size_t operator()(const NsMapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (size_t)k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+        h ^= (size_t)k.ld * 31 + (size_t)k.cols * 131 + (size_t)k.box_rows * 8191 + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+
 inline int ns_make_map_bf16(CUtensorMap* map, const void* ptr, unsigned long long rows, int cols, long long ld,
                             int box_rows, const char* who) {
+    static thread_local std::unordered_map<NsMapKey, CUtensorMap, NsMapKeyHash> known;
+    const NsMapKey key{ptr, rows, ld, cols, box_rows};
+    const auto hit = known.find(key);
+    if (hit != known.end()) {
+        *map = hit->second;
+        return NS_OK;
+    }
     NsEncodeTiledFn fn = ns_encode_fn();
     if (!fn) NS_FAIL(NS_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
     // the kernels address rows with signed 32-bit TMA coordinates
@@ -236,6 +266,8 @@ inline int ns_make_map_bf16(CUtensorMap* map, const void* ptr, unsigned long lon
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) NS_FAIL(NS_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with code %d", who, (int)r);
+    if (known.size() >= 8192) known.clear();
+    known.emplace(key, *map);
     return NS_OK;
 }
 

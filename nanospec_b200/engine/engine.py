@@ -10,6 +10,9 @@ head projection and sampling over the rows that end a request's known tokens, in
 
 from __future__ import annotations
 
+import time
+
+import numpy as np
 import torch
 
 from .. import ops
@@ -51,6 +54,10 @@ class Engine:
         # against its flops and bytes
         self.step_log: list[tuple[int, int, int, int]] | None = None
         self.d2h_bytes_last = 0
+        # host seconds spent composing batches (scheduler) and launching them (step description, copies, kernel
+        # launches), summed over the steps; neither includes waiting for the GPU
+        self.host_compose_s = 0.0
+        self.host_launch_s = 0.0
 
     # ---- profiling (CUDA events per phase, read once per step) -------------------------------
     def _mark(self, name: str) -> None:
@@ -108,18 +115,26 @@ class Engine:
         simply ignores the extra step's result."""
         if self._inflight is not None and not any(s.req.state == "running" for s in self._inflight.batch):
             self._inflight = None  # a step launched ahead for requests that have all ended meanwhile: nothing to read
+        t0 = time.perf_counter()
         if self._inflight is None:
             batch = self.sched.next_batch()
             if not batch:
                 return []
             self._mark("start")
+            t1 = time.perf_counter()
             self._inflight = self._launch(batch, None)
+            self.host_compose_s += t1 - t0
+            self.host_launch_s += time.perf_counter() - t1
         flight = self._inflight
         ahead = None
+        t0 = time.perf_counter()
         nxt = self._batch_ahead(flight)
         if nxt is not None:
+            t1 = time.perf_counter()
             ahead = self._launch(nxt, flight)
             self.launched_ahead += 1
+            self.host_compose_s += t1 - t0
+            self.host_launch_s += time.perf_counter() - t1
         finished = self._collect(flight)
         self._inflight = ahead
         self._after_step()
@@ -149,11 +164,21 @@ class Engine:
                     src.append(s.from_row)
                 row += len(s.tokens)
             take = (dst, prev.tok_dev, src)
-        hidden = self.runner.run(entries, take)
+        # the sampling options of the rows that sample travel with the step's description: [temperature | top_k |
+        # top_p | uniform], one value per row each (floats by their bits)
+        R = len(sampling)
+        options = np.empty(4 * R, dtype=np.int32)
+        as_f32 = options.view(np.float32)
+        as_f32[:R] = [s.req.params.temperature for s in sampling]
+        options[R: 2 * R] = [s.req.params.top_k for s in sampling]
+        as_f32[2 * R: 3 * R] = [s.req.params.top_p for s in sampling]
+        as_f32[3 * R:] = self._uniforms(sampling)
+        ctx, want_rows, _ = self.runner.build_context(entries, take, options)
+        hidden = self.runner.forward(ctx, want_rows)
         self._mark("forward")
         for s in batch:
             s.req.committed += len(s.tokens)
-        return self._score_launch(hidden, batch, sampling)
+        return self._score_launch(hidden, batch, sampling, ctx.extras["extra"])
 
     def _collect(self, flight) -> list[Request]:
         """Waits for the step's tokens and hands them to their requests."""
@@ -207,7 +232,7 @@ class Engine:
         free, planned = cache.free_pages(), [0] * len(cache.groups)
 
         def fits(req: Request, n: int) -> bool:
-            need = cache.need(req.id, req.committed + n)
+            need = cache.need_between(req.committed, req.committed + n)
             if any(nd + pl > fr for nd, pl, fr in zip(need, planned, free)):
                 return False
             for i, nd in enumerate(need):
@@ -237,7 +262,7 @@ class Engine:
     def _uniforms(self, sampling: list[Scheduled]) -> list[float]:
         # one uniform per sampled token from the request's own generator (engine/engine.py:283 in
         # the reference): results do not depend on what else is in the batch
-        return [float(torch.rand(1, generator=s.req.gen)) if s.req.params.temperature > 0 else 0.0 for s in sampling]
+        return [s.req.next_uniform() if s.req.params.temperature > 0 else 0.0 for s in sampling]
 
     def _score_buffers(self, rows: int):
         """Device and pinned host buffers for a step's sampled tokens and log-probs; two sets used in turn
@@ -253,18 +278,16 @@ class Engine:
             self._score_bufs[self._score_turn] = bufs
         return bufs
 
-    def _score_launch(self, hidden: torch.Tensor | None, batch: list[Scheduled], sampling: list[Scheduled]) -> "EagerFlight":
+    def _score_launch(self, hidden: torch.Tensor | None, batch: list[Scheduled], sampling: list[Scheduled],
+                      options: torch.Tensor) -> "EagerFlight":
         """Head projection and token choice for the rows of `hidden`, `head_chunk` rows at a time; the
-        results start their way to the host and are read by `_score_collect`."""
+        results start their way to the host and are read by `_score_collect`.  `options`: the rows' sampling
+        options on the device, as `_launch` laid them out."""
         if hidden is None or not sampling:
             return EagerFlight(batch, [], None, None, None, None, None)
         R = hidden.shape[0]
-        dev = self.device
-        P = [s.req.params for s in sampling]
-        temp = torch.tensor([p.temperature for p in P], dtype=torch.float32).to(dev, non_blocking=True)
-        top_k = torch.tensor([p.top_k for p in P], dtype=torch.int32).to(dev, non_blocking=True)
-        top_p = torch.tensor([p.top_p for p in P], dtype=torch.float32).to(dev, non_blocking=True)
-        u = torch.tensor(self._uniforms(sampling), dtype=torch.float32).to(dev, non_blocking=True)
+        temp, top_k = options[:R].view(torch.float32), options[R: 2 * R]
+        top_p, u = options[2 * R: 3 * R].view(torch.float32), options[3 * R: 4 * R].view(torch.float32)
         tok_dev, lp_dev, tok_host, lp_host, done = self._score_buffers(R)
         raw = [] if self.config.record_logits else None
         chunk = self.config.head_chunk

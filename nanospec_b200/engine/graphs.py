@@ -14,6 +14,8 @@ device buffer per step; the graph's kernels hold pointers into that device buffe
 
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import torch
 
@@ -57,7 +59,7 @@ class _Bucket:
         # them on the device, from the predecessor's sampled tokens (`out_token` of a bucket, or an eager step's)
         self.ids_host = torch.full((size,), -1, dtype=torch.int32).pin_memory()
         self.ids_dev = torch.full((size,), -1, dtype=torch.int32, device=runner.device)
-        self.row_sig: list[tuple | None] = [None] * size
+        self.table_off_c = (ctypes.c_int * max(n_groups, 1))(*self.table_off)
         self.copied = torch.cuda.Event()
         self.out_token = torch.zeros(size, dtype=torch.int32, device=runner.device)
         self.out_lp = torch.zeros(2, size, dtype=torch.float32, device=runner.device)
@@ -73,7 +75,7 @@ class _Bucket:
         # fixed parts of the description
         self.host_np[self.off["qo_indptr"]: self.off["qo_indptr"] + size + 1] = np.arange(size + 1, dtype=np.int32)
         self.host_np[self.off["want_rows"]: self.off["want_rows"] + size] = np.arange(size, dtype=np.int32)
-        self._fill_padding(0)
+        self._fill_padding(0, description=True)
         self.dev.copy_(self.host)
 
         def view(name: str, n: int, dtype=torch.int32) -> torch.Tensor:
@@ -95,14 +97,16 @@ class _Bucket:
                          view("u", size, torch.float32))
         self._capture(runner, pool)
 
-    def _fill_padding(self, first: int) -> None:
+    def _fill_padding(self, first: int, description: bool = False) -> None:
+        """Sampling options and token ids of the rows from `first` on; with `description` also their request (-1),
+        position, length and state slot, which a launch leaves to the cache manager's native side."""
         o, n = self.off, self.size
-        scratch_slot = self.scratch_slot
         self.ids_host[first:] = -1
-        self.host_np[o["token_req"] + first: o["token_req"] + n] = -1
-        self.host_np[o["positions"] + first: o["positions"] + n] = 0
-        self.host_np[o["kv_len"] + first: o["kv_len"] + n] = 0
-        self.host_np[o["slots"] + first: o["slots"] + n] = scratch_slot
+        if description:
+            self.host_np[o["token_req"] + first: o["token_req"] + n] = -1
+            self.host_np[o["positions"] + first: o["positions"] + n] = 0
+            self.host_np[o["kv_len"] + first: o["kv_len"] + n] = 0
+            self.host_np[o["slots"] + first: o["slots"] + n] = self.scratch_slot
         self.host_np[o["top_k"] + first: o["top_k"] + n] = 0
         self.host_f32[o["temperature"] + first: o["temperature"] + n] = 0.0
         self.host_f32[o["top_p"] + first: o["top_p"] + n] = 1.0
@@ -179,30 +183,17 @@ class DecodeGraphs:
         m = runner.manager
         B = len(batch)
         bk = self._bucket(self.bucket_size(B))
-        entries = [StepEntry(s.req.id, [0] if take is not None else s.tokens, [0]) for s in batch]
-        starts = [m.seq_len[e.req_id] for e in entries]
-        runner._reserve(entries)
+        req_ids = np.fromiter((s.req.id for s in batch), dtype=np.int64, count=B)
         bk.copied.synchronize()  # the previous copy out of the pinned buffers has finished
         o, hn, hf = bk.off, bk.host_np, bk.host_f32
-        hn[o["positions"]: o["positions"] + B] = starts
-        hn[o["token_req"]: o["token_req"] + B] = np.arange(B, dtype=np.int32)
-        hn[o["kv_len"]: o["kv_len"] + B] = [st + 1 for st in starts]
-        hn[o["slots"]: o["slots"] + B] = [m.state_slot(e.req_id) for e in entries]
+        # pages for one more position of every request (all or none), then positions, lengths, state slots, padding
+        # rows and every group's block-table rows, written by the cache manager's native side
+        m.pack_decode(req_ids, bk.size, runner.max_positions, hn, o, bk.table_off_c, bk.width)
         hn[o["top_k"]: o["top_k"] + B] = [s.req.params.top_k for s in batch]
         hf[o["temperature"]: o["temperature"] + B] = [s.req.params.temperature for s in batch]
         hf[o["top_p"]: o["top_p"] + B] = [s.req.params.top_p for s in batch]
         hf[o["u"]: o["u"] + B] = uniforms
         bk._fill_padding(B)
-        W = bk.width
-        for gi, toff in enumerate(bk.table_off):
-            for r, e in enumerate(entries):
-                pages = m.table(gi, e.req_id)
-                cacheable = len(bk.table_off) == 1 and m.groups[gi].spec.window == 0
-                sig = (e.req_id, batch[r].req.preemptions, len(pages), pages[-1] if pages else -1)
-                if cacheable and bk.row_sig[r] == sig:
-                    continue  # this row already holds this request's table
-                hn[toff + r * W: toff + r * W + len(pages)] = pages
-                bk.row_sig[r] = sig if cacheable else None
         t0 = t1 = None
         if self.timing is not None:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -231,8 +222,7 @@ class DecodeGraphs:
         if t1 is not None:
             t1.record()
             self.timing.append((t0, t1))
-        for e in entries:
-            m.trim(e.req_id)
+        m.trim_many(req_ids)
         return InFlight(batch, bk, turn, B, raw)
 
     def collect(self, flight: "InFlight"):

@@ -63,6 +63,7 @@ class Request:
     logprobs: list[TokenInfo] = field(default_factory=list)
     step_logits: list = field(default_factory=list)  # only with EngineConfig.record_logits
     peak_pages: list[int] | None = None  # the scheduler's note: most pages per cache group it can ever hold
+    _uniforms: list[float] = field(default_factory=list, repr=False)  # drawn ahead from `gen`, not yet used
 
     def __post_init__(self) -> None:
         self.gen = torch.Generator()
@@ -70,6 +71,14 @@ class Request:
             self.gen.manual_seed(self.params.seed)
         else:
             self.gen.seed()
+
+    def next_uniform(self) -> float:
+        """The next number of the request's own stream, the one that `torch.rand(1, generator=gen)` would give
+        (sched/scheduler.py:64,74-76 and engine/engine.py:283 in the reference): eight are drawn at a time, which
+        gives the same stream as single draws and costs an eighth of the calls."""
+        if not self._uniforms:
+            self._uniforms = torch.rand(8, generator=self.gen).tolist()[::-1]
+        return self._uniforms.pop()
 
     def tokens(self) -> list[int]:
         return self.prompt_ids + self.out_tokens
@@ -163,7 +172,7 @@ class Scheduler:
 
         def fits(req_id: int | None, cur: int, n: int) -> bool:
             nonlocal need
-            need = cache.need(req_id, cur + n)
+            need = cache.need_between(cur, cur + n)  # a live request holds exactly the pages of its `cur` positions
             return all(nd + pl <= fr for nd, pl, fr in zip(need, planned, free))
 
         def plan(req: Request, n: int) -> None:
@@ -179,7 +188,7 @@ class Scheduler:
             nonlocal budget
             for k, sch in enumerate(batch):
                 if sch.req is victim:
-                    for gi, nd in enumerate(cache.need(victim.id, victim.committed + len(sch.tokens))):
+                    for gi, nd in enumerate(cache.need_between(victim.committed, victim.committed + len(sch.tokens))):
                         planned[gi] -= nd
                     budget += len(sch.tokens)
                     del batch[k]
@@ -236,7 +245,7 @@ class Scheduler:
                 if any(p > h for p, h in zip(peak, headroom)):
                     break
                 headroom = [h - p for h, p in zip(headroom, peak)]
-                need = cache.need(None, n)
+                need = cache.need_between(0, n)
             elif not fits(None, 0, n):
                 break
             self.waiting.popleft()
@@ -267,7 +276,7 @@ class Scheduler:
                     owed[gi] += max(0, pk - held)
             return all(p <= f - o for p, f, o in zip(self._peak(req), free, owed))
         n = min(req.pending, self.prefill_chunk, self.max_step_tokens)
-        return all(nd <= fr for nd, fr in zip(cache.need(None, n), free))
+        return all(nd <= fr for nd, fr in zip(cache.need_between(0, n), free))
 
     # ---- transitions -----------------------------------------------------------------------
     def finish(self, req: Request) -> None:

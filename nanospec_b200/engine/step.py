@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..cache import CacheManager, CacheStorage, PoolExhausted
+from ..cache import CacheManager, CacheStorage
 from ..parts.context import StepContext, Workspace
 from ..parts.model import DecoderModel
 
@@ -55,6 +55,11 @@ class _Staging:
             self.bufs[i] = buf
         return buf, i
 
+    def replace(self, i: int, n_ints: int) -> torch.Tensor:
+        """A larger buffer in place of buffer `i`, which the caller holds and no copy reads."""
+        self.bufs[i] = torch.empty(n_ints, dtype=torch.int32).pin_memory()
+        return self.bufs[i]
+
     def mark(self, i: int) -> None:
         ev = self.events[i] or torch.cuda.Event()
         ev.record()
@@ -76,6 +81,7 @@ class ModelRunner:
         self.block_size = block_size
         self.max_positions = model.recipe.max_positions
         self._staging = _Staging()
+        self._staging_ints = 1 << 16
         self._meta_dev: torch.Tensor | None = None
         self.h2d_bytes_last = 0
 
@@ -87,88 +93,59 @@ class ModelRunner:
         self.manager.end(req_id)
 
     # ---- building the batch ----------------------------------------------------------------
-    def _reserve(self, entries: list[StepEntry]) -> None:
-        done: list[tuple[int, int]] = []
-        try:
-            for e in entries:
-                if not e.tokens:
-                    raise ValueError(f"request {e.req_id} brings no tokens to the step")
-                if self.manager.seq_len[e.req_id] + len(e.tokens) > self.max_positions:
-                    raise ValueError(
-                        f"request {e.req_id} would reach {self.manager.seq_len[e.req_id] + len(e.tokens)} positions; "
-                        f"the model's limit is {self.max_positions}")
-                before = self.manager.seq_len[e.req_id]
-                self.manager.extend(e.req_id, len(e.tokens))
-                done.append((e.req_id, before))
-        except (PoolExhausted, ValueError):
-            for rid, before in reversed(done):
-                self.manager.rollback(rid, before)
-            raise
-
     def build_context(self, entries: list[StepEntry], take: tuple[list[int], torch.Tensor, list[int]] | None = None,
-                      ) -> tuple[StepContext, torch.Tensor | None, int]:
-        """Reserves pages, lays the step description out in one pinned buffer and copies it
-        to the device once.  Returns (context, wanted rows on the device or None, n wanted).
+                      extra: np.ndarray | None = None) -> tuple[StepContext, torch.Tensor | None, int]:
+        """Reserves pages (for every entry, or for none: `PoolExhausted` and `ValueError` leave the cache as it
+        was), lays the step description out in one pinned buffer - in native code, from the block tables that
+        live there - and copies it to the device once.  Returns (context, wanted rows on the device or None, n wanted).
         `take` = (token rows of this step, an int32 device tensor, rows of it): those token ids are not
-        known to the host yet and are taken from the tensor on the device (the entries carry a placeholder)."""
-        ids = [e.req_id for e in entries]
-        if len(set(ids)) != len(ids):
-            raise ValueError("a request may appear once in a step")
-        vocab = self.model.vocab_size
+        known to the host yet and are taken from the tensor on the device (the entries carry a placeholder).
+        `extra`: int32 values that travel with the description (`ctx.extras["extra"]` is their place on the device):
+        everything a step needs from the host goes in this one copy from pinned memory, since a copy from ordinary
+        memory would make the host wait for all the work queued before it."""
         m = self.manager
         B = len(entries)
+        req_ids = np.fromiter((e.req_id for e in entries), dtype=np.int64, count=B)
+        if len(set(req_ids.tolist())) != B:
+            raise ValueError("a request may appear once in a step")
         q_lens = [len(e.tokens) for e in entries]
         N = sum(q_lens)
-        ids_np = np.empty(N, dtype=np.int64)
+        ids_np = np.empty(max(N, 1), dtype=np.int32)
+        want_rows: list[int] = []
         at = 0
         for e, n in zip(entries, q_lens):
+            if n == 0:
+                raise ValueError(f"request {e.req_id} brings no tokens to the step")
             if n == 1:
                 ids_np[at] = e.tokens[0]
             else:
                 ids_np[at: at + n] = e.tokens
-            at += n
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.req_id} wants logits at place {w} of {n} tokens")
-        if N and (ids_np.min() < 0 or ids_np.max() >= vocab):
-            bad = int(ids_np[(ids_np < 0) | (ids_np >= vocab)][0])
+                want_rows.append(at + w)
+            at += n
+        vocab = self.model.vocab_size
+        if N and (ids_np[:N].min() < 0 or ids_np[:N].max() >= vocab):
+            bad = int(ids_np[:N][(ids_np[:N] < 0) | (ids_np[:N] >= vocab)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
-        starts = [m.seq_len[e.req_id] for e in entries]
-        self._reserve(entries)
-
-        kv_lens = [s + n for s, n in zip(starts, q_lens)]
         q_lens_np = np.asarray(q_lens, dtype=np.int32)
-        qo_indptr = np.zeros(B + 1, dtype=np.int32)
-        np.cumsum(q_lens_np, out=qo_indptr[1:])
-        token_req = np.repeat(np.arange(B, dtype=np.int32), q_lens_np)
-        # token i of request b sits at position starts[b] + (i - qo_indptr[b])
-        positions = np.arange(N, dtype=np.int32) + np.repeat(np.asarray(starts, dtype=np.int32) - qo_indptr[:-1], q_lens_np)
-        want_rows = [int(qo_indptr[b]) + w for b, e in enumerate(entries) for w in e.want]
-        slots = [m.state_slot(e.req_id) for e in entries]
-        tables, widths = [], []
-        for gi in range(len(m.groups)):
-            rows = [m.table(gi, e.req_id) for e in entries]
-            width = max(1, max(len(r) for r in rows))
-            table = np.zeros((B, width), dtype=np.int32)
-            for b, r in enumerate(rows):
-                table[b, : len(r)] = r
-            tables.append(table.reshape(-1))
-            widths.append(width)
-
+        want_np = np.asarray(want_rows, dtype=np.int32)
         take_dst = np.asarray(take[0] if take else [], dtype=np.int32)
         take_src = np.asarray(take[2] if take else [], dtype=np.int32)
-        parts = [ids_np.astype(np.int32), positions, token_req, qo_indptr, np.asarray(kv_lens, dtype=np.int32),
-                 np.asarray(slots, dtype=np.int32), np.asarray(want_rows, dtype=np.int32), take_dst, take_src, *tables]
-        offsets, total = [], 0
-        for p in parts:
-            offsets.append(total)
-            total += len(p) + (-len(p) % 4)  # 16-byte aligned sections
-        host, turn = self._staging.get(total)
-        host_np = host.numpy()
-        for off, p in zip(offsets, parts):
-            host_np[off: off + len(p)] = p
+        extra_np = np.zeros(0, dtype=np.int32) if extra is None else np.ascontiguousarray(extra, dtype=np.int32)
+        host, turn = self._staging.get(self._staging_ints)
+        while True:
+            try:
+                offsets, widths, counts, total, max_q, max_kv = m.pack_step(
+                    req_ids, q_lens_np, ids_np, want_np, take_dst, take_src, extra_np, (ops.TILE_Q, ops.TILE_Q_TCGEN05),
+                    self.max_positions, host.numpy(), host.numel())
+                break
+            except BufferError as need:  # the description is larger than any before: a larger pinned buffer, once
+                self._staging_ints = 2 * int(need.args[0])
+                host = self._staging.replace(turn, self._staging_ints)
         if self._meta_dev is None or self._meta_dev.numel() < total:
-            self._meta_dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
+            self._meta_dev = torch.empty(max(2 * total, 4096), dtype=torch.int32, device=self.device)
         dev = self._meta_dev
         dev[:total].copy_(host[:total], non_blocking=True)
         self._staging.mark(turn)
@@ -177,10 +154,12 @@ class ModelRunner:
         def view(i: int, n: int) -> torch.Tensor:
             return dev[offsets[i]: offsets[i] + n]
 
-        if take and len(take_dst):
+        if len(take_dst):
             ops.take_ids(view(0, N), view(7, len(take_dst)), take[1], view(8, len(take_src)))
-        group_tables = [view(9 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
+        group_tables = [view(13 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
         self.storage.zero_state_slots(m.take_fresh_slots())
+        host_np = host.numpy()
+        kv_lens = host_np[offsets[4]: offsets[4] + B].tolist()
         ctx = StepContext(
             n_tokens=N, n_requests=B,
             token_ids=view(0, N), positions=view(1, N), token_req=view(2, N), qo_indptr=view(3, B + 1),
@@ -188,8 +167,19 @@ class ModelRunner:
             q_lens=q_lens, kv_lens=kv_lens,
             lanes=self.storage.lane_views(group_tables),
             workspace=self.workspace, dtype=self.dtype, device=self.device,
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens), state_slots_host=slots,
+            max_q_len=max_q, max_kv_len=max_kv, state_slots_host=host_np[offsets[5]: offsets[5] + B].tolist(),
         )
+        ctx.extras["req_ids"] = req_ids
+        ctx.extras["extra"] = view(12, len(extra_np))
+        # which token rows decode and the query tiles of the prompt portions (ops.attention reads this)
+        n_decode, n_a, n_b, max_kv_decode = counts
+        ctx.extras["attention_plan"] = {
+            "n_decode": n_decode,
+            "decode_rows": None if n_decode == N or not n_decode else view(9, n_decode),
+            "tiles": view(10, 2 * n_a).view(n_a, 2) if n_a else None,
+            "tiles_tc": view(11, 2 * n_b).view(n_b, 2) if n_b else None,
+            "max_kv_len": max_kv_decode or None,
+        }
         n_want = len(want_rows)
         return ctx, (view(6, n_want) if n_want else None), n_want
 
@@ -199,9 +189,12 @@ class ModelRunner:
         order of the entries and of their `want` lists ([n_wanted, hidden]), or None.
         `take`: token ids that are still on the device (see build_context)."""
         ctx, want_rows, n_want = self.build_context(entries, take)
+        return self.forward(ctx, want_rows)
+
+    def forward(self, ctx: StepContext, want_rows: torch.Tensor | None) -> torch.Tensor | None:
+        """The model over a context that `build_context` made, then the pages that windows have passed go back."""
         hidden = self.model.forward(ctx, want_rows)  # None when nothing is wanted: the blocks still fill the cache
-        for e in entries:
-            self.manager.trim(e.req_id)
+        self.manager.trim_many(ctx.extras["req_ids"])
         return hidden
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:

@@ -10,7 +10,7 @@ import random
 
 import pytest
 
-from nanospec_b200.cache import RELEASED, CacheManager, PagePool, PoolExhausted, SlotPool
+from nanospec_b200.cache import RELEASED, CacheManager, PoolExhausted
 from nanospec_b200.parts import CacheNeed, StateNeed
 
 
@@ -121,21 +121,21 @@ def test_double_begin_double_end_and_double_free_are_caught():
     m.end(0)
     with pytest.raises(KeyError):
         m.end(0)
-    p = PagePool(4)
-    got = p.take(2)
-    p.give(got)
-    with pytest.raises(AssertionError):
-        p.give(got[:1])
-    with pytest.raises(AssertionError):
-        p.give([9])
+    with pytest.raises(KeyError):
+        m.extend(0, 1)
+    assert m.free_pages() == [8, ] and m.groups[0].pool.free_pages()[-1] == 0  # the page freed last goes out next
+    m.check()
 
 
 def test_state_slots():
-    s = SlotPool(2)
-    assert s.acquire(10) == 0 and s.acquire(11) == 1
+    s = manager(slots=2)
+    s.begin(10), s.begin(11)
+    assert s.state_slot(10) == 0 and s.state_slot(11) == 1 and s.scratch_slot == 2
     with pytest.raises(PoolExhausted):
-        s.acquire(12)
-    assert s.release(10) == 0 and s.acquire(12) == 0
+        s.begin(12)
+    s.end(10)
+    s.begin(12)
+    assert s.state_slot(12) == 0 and s.slots.num_free == 0  # the slot given back last goes out next
     s.check()
     m = manager(slots=1)
     m.begin(0)
@@ -184,4 +184,65 @@ def test_random_orders_keep_every_invariant(seed, window):
         m.begin(10_000), m.extend(10_000, 32)
         t = m.table(0, 10_000)
         assert any(b != a + 1 for a, b in zip(t, t[1:])), t
+    m.check()
+
+
+def test_a_steps_description_is_packed_natively_and_reserves_all_or_nothing():
+    """`pack_step`: pages for every entry or for none, and the layout that the kernels read (positions continue
+    each request's sequence, a block table per group as wide as the longest one, sections on 16-byte bounds)."""
+    import numpy as np
+
+    m = CacheManager([(CacheNeed(2, 8, 0), None), (CacheNeed(1, 16, 0), None)], num_blocks=6, block_size=4, num_state_slots=3)
+    m.begin(5), m.begin(9)
+    m.extend(5, 6)
+    buf = np.full(256, -7, dtype=np.int32)
+
+    def pack(ids, q_lens, tokens, want=(), cap=256, limit=64):
+        a = lambda x, t=np.int32: np.asarray(list(x), dtype=t)
+        return m.pack_step(a(ids, np.int64), a(q_lens), a(tokens), a(want), a(()), a(()), a((11, 12, 13)), (2, 4), limit, buf, cap)
+
+    offsets, widths, counts, total, max_q, max_kv = pack([5, 9], [1, 3], [40, 41, 42, 43], want=[0, 3])
+    assert (max_q, max_kv, widths) == (3, 7, [2, 2]) and all(o % 4 == 0 for o in offsets) and total <= 256
+    # one request decodes (row 0, 7 positions); the other's 3 tokens make two query tiles of 2 and one of 4
+    assert counts == [1, 2, 1, 7]
+    sec = lambda i, n: buf[offsets[i]: offsets[i] + n].tolist()
+    assert sec(0, 4) == [40, 41, 42, 43] and sec(1, 4) == [6, 0, 1, 2] and sec(2, 4) == [0, 1, 1, 1]
+    assert sec(3, 3) == [0, 1, 4] and sec(4, 2) == [7, 3] and sec(5, 2) == [0, 1] and sec(6, 2) == [0, 3]
+    assert sec(9, 1) == [0] and sec(10, 4) == [1, 2, 1, 0] and sec(11, 2) == [1, 0] and sec(12, 3) == [11, 12, 13]
+    for gi in (0, 1):
+        table = buf[offsets[13 + gi]: offsets[13 + gi] + 4].reshape(2, 2).tolist()
+        assert table[0] == m.table(gi, 5) and table[1] == m.table(gi, 9) + [0]
+    assert m.seq_len[5] == 7 and m.seq_len[9] == 3 and m.free_pages() == [3, 3]
+    m.check()
+    # the second entry does not fit: the first entry's reservation is undone as well
+    with pytest.raises(PoolExhausted):
+        pack([5, 9], [2, 14], list(range(16)))
+    assert m.seq_len[5] == 7 and m.seq_len[9] == 3 and m.free_pages() == [3, 3]
+    with pytest.raises(ValueError, match="limit is 8"):
+        pack([5], [2], [1, 2], limit=8)
+    with pytest.raises(BufferError) as e:
+        pack([5], [1], [1], cap=8)
+    assert e.value.args[0] > 8 and m.seq_len[5] == 7
+    with pytest.raises(KeyError):
+        pack([77], [1], [1])
+    m.check()
+
+
+def test_a_decode_steps_description_for_a_graph_bucket():
+    import ctypes
+
+    import numpy as np
+
+    m = manager(num_blocks=8, block_size=4, lanes=1, slots=3)
+    m.begin(3), m.begin(4)
+    m.extend(3, 4), m.extend(4, 2)
+    buf = np.full(64, -7, dtype=np.int32)
+    off = {"positions": 0, "token_req": 4, "kv_len": 8, "slots": 12}
+    m.pack_decode(np.asarray([4, 3], dtype=np.int64), 4, 64, buf, off, (ctypes.c_int * 1)(16), 5)
+    assert buf[0:4].tolist() == [2, 4, 0, 0] and buf[4:8].tolist() == [0, 1, -1, -1]       # padding rows: request -1
+    assert buf[8:12].tolist() == [3, 5, 0, 0] and buf[12:16].tolist() == [1, 0, 3, 3]        # ... and the scratch slot
+    assert buf[16:17].tolist() == m.table(0, 4) and buf[21:23].tolist() == m.table(0, 3)    # request 3 took a second page
+    assert m.seq_len[3] == 5 and m.seq_len[4] == 3
+    with pytest.raises(ValueError, match="wider"):
+        m.pack_decode(np.asarray([3], dtype=np.int64), 4, 64, buf, off, (ctypes.c_int * 1)(16), 1)
     m.check()

@@ -221,3 +221,13 @@ def test_could_admit_says_what_next_batch_does(admission):
                     if len(sch.req.out_tokens) >= sch.req.params.max_tokens:
                         s.finish(sch.req)
             s.cache.check()
+
+
+def test_a_requests_uniforms_are_the_stream_of_single_draws():
+    import torch
+
+    from nanospec_b200.engine import Request, SamplingParams
+
+    r = Request(0, [1], SamplingParams(seed=5))
+    g = torch.Generator().manual_seed(5)
+    assert [r.next_uniform() for _ in range(21)] == [float(torch.rand(1, generator=g)) for _ in range(21)]
