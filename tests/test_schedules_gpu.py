@@ -483,3 +483,77 @@ def test_command_line_generate_and_bench(tiny_folders):
     assert all(r["tok_s"] > 0 and abs(r["tpot_ms"] - 1000 * r["bs"] / r["tok_s"]) < 0.05 * r["tpot_ms"] for r in lines)
     table = _cli("table", stdin=env_out.stdout)
     assert table.splitlines()[0].startswith("| engine |") and "| nanospec_b200 | nospec | 2 |" in table
+
+
+# ---------------------------------------------------------------------------------------------------
+# layers with different needs in one model: all keys beside a window of them
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_beside_layers_with_all_keys_through_the_engine(dtype, tmp_path):
+    """A recipe registered from here: layer 0 reads every key, layers 1 and 2 the last 24 only.  The two kinds form
+    two cache groups with pools and block tables of their own; the windowed group gives pages back while its
+    requests run (they decode far past what it could hold otherwise) and hands them out again.  Generation through
+    graphs and through eager steps, portions of 32, every step's logits against the plain implementation with the
+    same windows."""
+    import dataclasses
+
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.cache import RELEASED
+    from nanospec_b200.config import Architecture, LlamaConfig, PartSpec, register_architecture, registered_architectures
+    from nanospec_b200.weights import write_random_model
+
+    window = 24
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        layers = list(r.layers)
+        for i in (1, 2):
+            m = layers[i].mixer
+            layers[i] = dataclasses.replace(layers[i], mixer=PartSpec(m.kind, {**m.params, "window": window}))
+        return dataclasses.replace(r, architecture="WindowedForCausalLM", layers=tuple(layers))
+
+    if "WindowedForCausalLM" not in registered_architectures():  # the test runs once per dtype
+        register_architecture(Architecture("WindowedForCausalLM", "windowed-test", LlamaConfig.from_hf, recipe))
+    cfg_t = LlamaConfig(vocab_size=700, hidden_size=256, intermediate_size=384, num_hidden_layers=3, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=256)
+    hf = cfg_t.to_hf()
+    hf["architectures"] = ["WindowedForCausalLM"]
+    write_random_model(tmp_path, hf, seed=12)
+    pcfg, w = plain.read_folder(tmp_path)
+    dt = DTYPES[dtype]
+    model = load(tmp_path, dt)
+    assert [n[0].window for n in model.lane_needs()] == [0, window, window]
+
+    def plain_logits(ids):
+        positions = torch.arange(len(ids))
+        inv = plain.plain_inv_freq(64, 10000.0, None)
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        for i in range(3):
+            p = f"model.layers.{i}."
+            h = plain.plain_rmsnorm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+            x = x + plain.plain_attention_block(h, w, p + "self_attn.", pcfg, positions, inv, window if i else 0)
+            x = x + plain.plain_mlp(plain.plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"]), w, p + "mlp.")
+        return plain.plain_rmsnorm(x, w["model.norm.weight"], pcfg["eps"]) @ w["lm_head.weight"].T
+
+    prompts = [random_ids(n, 700, seed=60 + n) for n in (50, 9, 120)]
+    limits = [70, 40, 30]
+    page = 8
+    for graphs in (True, False):
+        eng = engine(model, num_blocks=40, block_size=page, cuda_graphs=graphs, record_logits=True, prefill_chunk=32, max_admit=2)
+        assert len(eng.cache.groups) == 2 and eng.cache.groups[1].spec.window == window
+        reqs = [eng.add(p, params(max_tokens=n)) for p, n in zip(prompts, limits)]
+        most_held, released_seen = 0, False
+        while eng.sched.has_work:
+            eng.step()
+            eng.cache.check()
+            for r in reqs:
+                if r.state == "running":
+                    most_held = max(most_held, eng.cache.held_pages(r.id)[1])
+                    released_seen |= RELEASED in eng.cache.table(1, r.id)
+        # window - 1 + a portion of 32 positions, and one page more for alignment: far less than the 19 pages of 150 positions
+        assert most_held <= -(-(window - 1 + 32) // page) + 1 and released_seen
+        assert eng.cache.free_pages() == [40, 40] and eng.cache.live == []
+        for i, (req, prompt) in enumerate(zip(reqs, prompts)):
+            ids = list(prompt) + req.out_tokens
+            want = plain_logits(ids[:-1])[len(prompt) - 1:].numpy()
+            check_rows(torch.stack(req.step_logits).numpy(), want, dt, f"windowed layers, {dtype}, graphs={graphs}, request {i}")
