@@ -102,28 +102,26 @@ def cmd_bench(args) -> int:
     g = torch.Generator().manual_seed(0)
     base = [torch.randint(0, model.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(args.prompts)]
     prompts = [p for p in base for _ in range(args.n_samples)]
-    for bs in args.bs:
-        for run in range(args.runs):
-            args.max_running = bs
-            args.max_admit = min(bs, 8)  # the reference admits at most 8 new prompts per step (bench/run.py:79)
-            need = bs * (-(-(args.prompt_len + args.max_tokens) // args.block_size) + 1)
-            engine = _engine(model, args, need)
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            reqs = [engine.add(p, SamplingParams(args.max_tokens, temperature=args.temperature, seed=i, ignore_eos=True))
-                    for i, p in enumerate(prompts)]
-            while engine.sched.has_work:
-                engine.step()
-            torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            n_out = sum(len(r.out_tokens) for r in reqs)
-            print(json.dumps({
-                "engine": "nanospec_b200", "config": "nospec", "bs": bs, "prompts": len(prompts), "out_tokens": n_out,
-                "tok_s": round(n_out / dt, 1), "tpot_ms": round(1000 * dt / (n_out / bs), 2), "run": run,
-                "temperature": args.temperature, "gpu": torch.cuda.get_device_name(0), "dtype": args.dtype,
-                "steps": engine.steps, "data": "seeded uniform random token ids"}), flush=True)
-            del engine
-            torch.cuda.empty_cache()
+    # one engine per (batch size, run), as the reference's harness builds them (bench/run.py:75-91): `bs` live requests at
+    # most and at most 8 admissions per step; the clock covers adding every prompt and stepping until none is left
+    for bs, run in ((bs, run) for bs in args.bs for run in range(args.runs)):
+        args.max_running, args.max_admit = bs, min(bs, 8)
+        pages_each = -(-(args.prompt_len + args.max_tokens) // args.block_size) + 1
+        engine = _engine(model, args, bs * pages_each)
+        plist = [SamplingParams(args.max_tokens, temperature=args.temperature, seed=i, ignore_eos=True) for i in range(len(prompts))]
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        outs = engine.generate(prompts, plist)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - started
+        n_out = sum(len(o) for o in outs)
+        print(json.dumps({
+            "engine": "nanospec_b200", "config": "nospec", "bs": bs, "prompts": len(prompts), "out_tokens": n_out,
+            "tok_s": round(n_out / seconds, 1), "tpot_ms": round(1000 * seconds / (n_out / bs), 2), "run": run,
+            "temperature": args.temperature, "gpu": torch.cuda.get_device_name(0), "dtype": args.dtype,
+            "steps": engine.steps, "data": "seeded uniform random token ids"}), flush=True)
+        del engine
+        torch.cuda.empty_cache()
     return 0
 
 

@@ -28,12 +28,12 @@ from ..cache import CacheManager
 
 @dataclass(frozen=True)
 class SamplingParams:
-    max_tokens: int = 128
-    temperature: float = 0.0  # 0 = greedy
-    top_k: int = 0            # 0 = off
-    top_p: float = 1.0
-    seed: int | None = None   # per-request generator; None = random
-    logprobs: bool = False    # fill Request.logprobs
+    max_tokens: int = 128     # most new tokens of the request
+    temperature: float = 0.0  # zero picks the largest raw logit; otherwise logits are divided by it before the draw
+    top_k: int = 0            # keep only the k most likely tokens; zero keeps all
+    top_p: float = 1.0        # keep the smallest set of most likely tokens whose probability reaches this
+    seed: int | None = None   # seeds the request's own generator; without one the stream is unpredictable
+    logprobs: bool = False    # record a TokenInfo for every emitted token
     ignore_eos: bool = False  # keep generating past an end-of-sequence token (benchmarks on random weights)
 
     def __post_init__(self) -> None:
@@ -46,8 +46,9 @@ class SamplingParams:
 @dataclass(slots=True)
 class TokenInfo:
     token: int
-    logprob: float         # log p(token) under the raw logits at temperature 1
-    sample_logprob: float  # log-prob under the (temperature, top-k, top-p) distribution it was drawn from; 0 when greedy
+    logprob: float         # the token's log-probability under the unprocessed logits
+    sample_logprob: float  # its log-probability under the distribution that the draw used (after temperature, top-k
+                           # and top-p); a greedy pick records 0
 
 
 @dataclass
@@ -56,10 +57,10 @@ class Request:
     prompt_ids: list[int]
     params: SamplingParams
     out_tokens: list[int] = field(default_factory=list)
-    state: str = "waiting"  # waiting | running | done
-    committed: int = 0      # cache positions written; tokens()[committed:] are still to be fed
+    state: str = "waiting"  # "waiting" in the queue, "running" with cache pages, "done"
+    committed: int = 0      # positions of this request that the cache holds; tokens()[committed:] have not run yet
     preemptions: int = 0
-    gen: torch.Generator = None  # CPU generator seeded per request: draws do not depend on the batch
+    gen: torch.Generator = None  # the request's own host generator, so that what it draws is the same in any batch
     logprobs: list[TokenInfo] = field(default_factory=list)
     step_logits: list = field(default_factory=list)  # only with EngineConfig.record_logits
     peak_pages: list[int] | None = None  # the scheduler's note: most pages per cache group it can ever hold
