@@ -93,12 +93,13 @@ def _decode_point(net, batch: int, context: int, steps: int, warmup: int, repeat
     total = warmup + repeats * steps + 16
     num_blocks = batch * (-(-(context + total) // page) + 1) + 8
     eng = Engine(net, EngineConfig(num_blocks, page, max_admit=min(batch, 8), max_running=batch, cuda_graphs=graphs))
+    sampler = sampler_cls()
+    sampler.start()
     reqs = _prime(eng, SamplingParams, batch, context, total, net.config.vocab_size)
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()
-    sampler = sampler_cls()
-    sampler.start()
+    sampler.mark()
     dev_ms, host_s = [], []
     for _ in range(repeats):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

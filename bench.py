@@ -89,6 +89,12 @@ class ClockSampler:
     def __init__(self) -> None:
         self.rows: list[list[str]] = []
         self.proc = None
+        self.first = 0
+
+    def mark(self) -> None:
+        """The timed region begins: samples taken before now (nvidia-smi needs a moment to start, so it is started
+        ahead of the warm-up) do not count, except the last one when no later sample exists."""
+        self.first = len(self.rows)
 
     def start(self) -> None:
         try:
@@ -111,10 +117,11 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        rows = self.rows[self.first:] or self.rows[-1:]
+        sm = sorted(int(r[0]) for r in rows if len(r) >= 6 and r[0].isdigit())
+        mx = [int(r[1]) for r in rows if len(r) >= 6 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
                 "samples": len(sm)}
 
@@ -194,14 +201,15 @@ def time_decode(eng, batch: int, steps: int, warmup: int, repeats: int) -> dict:
 
     from nanospec_b200.ops import lib
 
+    sampler = ClockSampler()
+    sampler.start()
     reqs = prime(eng, batch, CONTEXT, max_tokens=warmup + repeats * steps + 8)
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()
     bucket = eng.graphs.buckets[eng.graphs.bucket_size(batch)]
     launches0, replays0 = lib.launch_count(), eng.graphs.replays
-    sampler = ClockSampler()
-    sampler.start()
+    sampler.mark()
     dev_ms, host_s = [], []
     for _ in range(repeats):
         eng.graphs.timing = []
@@ -233,9 +241,10 @@ def time_prefill(eng, warmup: int, iters: int) -> tuple[float, dict]:
     g = torch.Generator().manual_seed(123)
     times = []
     sampler = ClockSampler()
+    sampler.start()
     for i in range(warmup + iters):
         if i == warmup:
-            sampler.start()
+            sampler.mark()
         ids = torch.randint(0, eng.model.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
         req = eng.add(ids, SamplingParams(max_tokens=1, ignore_eos=True))
         torch.cuda.synchronize()
