@@ -71,16 +71,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t q_smem = base;                                   // [tile]
     const uint32_t kv_smem = q_smem + kTiles * kQBytes;             // [stage][K | V]
     const uint32_t bar0 = kv_smem + kKvStages * 2 * kKBytes;
-    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], s_free[2], p_ready[2], o_done
+    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full[2], s_free[2], p_ready[2], o_done, o_final
     const uint32_t q_full = bar0;
     auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
-    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 7 + which); };
+    auto tile_bar = [&](int t, int which) { return bar0 + 8u * (1 + 2 * kKvStages + t * 8 + which); };
     auto s_full = [&](int t, int b) { return tile_bar(t, b); };
     auto s_free = [&](int t, int b) { return tile_bar(t, 2 + b); };
     auto p_ready = [&](int t, int b) { return tile_bar(t, 4 + b); };
     auto o_done = [&](int t) { return tile_bar(t, 6); };
-    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 7);
+    // Completed once, by the product of the tile's last block.  The output must not be read on o_done's parity: a
+    // softmax warp may finish its last block while the product of the block before it is still waiting for the
+    // tile's slower warps, and a parity wait two phases ahead of the barrier returns at once.
+    auto o_final = [&](int t) { return tile_bar(t, 7); };
+    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles * 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads vary fastest: the host lists the tiles with the most keys first, and blocks are
@@ -102,6 +106,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mbar_init(p_ready(t, b), 128);
             }
             mbar_init(o_done(t), 1);
+            mbar_init(o_final(t), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -214,6 +219,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (elect_one()) {
                     umma_commit(o_done(t));      // this tile's accumulator holds blocks 0..j
                     umma_commit(s_free(t, b));   // and S[t][b] may take the scores of block j+2
+                    if (j == nblk_t[t] - 1) umma_commit(o_final(t));  // the tile's accumulator is complete
                 }
             }
             // The stage's values have been read by every tile; its keys were read by the scores of block j,
@@ -302,9 +308,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tc_fence_before();
             mbar_arrive(p_ready(t, b));
         }
-        if (ok && my_blocks > 0) {
-            ok = mbar_wait_warp(o_done(t), (uint32_t)(my_blocks - 1) & 1u);
-        }
+        if (ok && my_blocks > 0) ok = mbar_wait_warp(o_final(t), 0);
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, kErrAttnSoftmax);
         } else if (my_blocks > 0) {

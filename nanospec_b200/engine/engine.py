@@ -206,8 +206,17 @@ class Engine:
         None when that cannot be said without its tokens (then the next step is composed by the
         scheduler, after this one has been collected)."""
         cfg = self.config
-        if not cfg.lookahead or cfg.record_logits or cfg.profile or self.sched.could_admit():
-            return None  # (somebody who waits and cannot be admitted as things stand waits one step longer at most)
+        if not cfg.lookahead or cfg.record_logits or cfg.profile:
+            return None
+        if self.sched.could_admit():
+            # Somebody waits who fits: the scheduler composes the next batch, admissions included, on the assumption
+            # that every request of the step in flight goes on.  (With optimistic admission it declines: composing
+            # could take pages back from a request whose tokens are not known yet.)
+            running = self.sched.running
+            if len(flight.batch) != len(running) or any(s.req.state != "running" for s in flight.batch):
+                return None
+            rows = {id(s): i for i, s in enumerate(flight.sampling)}
+            return self.sched.next_batch(ahead={id(s.req): rows[id(s)] for s in flight.batch if s.samples}) or None
         cache, running = self.cache, self.sched.running
         # every running request is in the step in flight; the next batch has them in the scheduler's order
         # (decoding ones first, then portions, each oldest first), and everything must fit

@@ -158,9 +158,18 @@ class Scheduler:
         self.waiting.append(req)
 
     # ---- one step's batch -----------------------------------------------------------------
-    def next_batch(self) -> list[Scheduled]:
+    def next_batch(self, ahead: dict[int, int] | None = None) -> list[Scheduled] | None:
         """Decoding requests first (one token each), then portions of running prompts, then
-        admissions; all under the token budget and the pages that are free."""
+        admissions; all under the token budget and the pages that are free.
+
+        `ahead`: the batch is composed while a step is still in flight.  It maps id(request) to the row of that
+        step that samples the request's next token: such a request brings a placeholder token that the step takes
+        on the device (`Scheduled.from_row`), unless the token in flight is its last.  Requests that the step in
+        flight turns out to have ended simply ignore their row of this one; admissions count them as still
+        running, which errs on the safe side.  Only with worst-case reservation, where composing a batch never
+        takes pages back from anybody: otherwise None is returned and nothing has changed."""
+        if ahead is not None and self.admission != "reserve":
+            return None
         cache = self.cache
         budget = self.max_step_tokens
         planned = [0] * len(cache.groups)  # pages this step's entries will take
@@ -181,8 +190,11 @@ class Scheduler:
             nonlocal budget
             for i, nd in enumerate(need):
                 planned[i] += nd
-            toks = req.token_slice(req.committed, req.committed + n)
-            batch.append(Scheduled(req, toks, samples=(n == req.pending)))
+            if ahead is not None and id(req) in ahead:
+                batch.append(Scheduled(req, [0], True, from_row=ahead[id(req)]))
+            else:
+                toks = req.token_slice(req.committed, req.committed + n)
+                batch.append(Scheduled(req, toks, samples=(n == req.pending)))
             budget -= n
 
         def unplan(victim: Request) -> None:
@@ -198,13 +210,19 @@ class Scheduler:
         # 1. running requests: those that decode first (one token each), then portions of
         #    prompts, each oldest first; when pages run out the newest running request is preempted
         preempted = False
-        order = [r for r in self.running if r.pending == 1] + [r for r in self.running if r.pending > 1]
+
+        def pending(r: Request) -> int:
+            if ahead is not None and id(r) in ahead:  # its next token is being sampled: one more, unless that one is its last
+                return 1 if len(r.out_tokens) + 1 < r.params.max_tokens else 0
+            return r.pending
+
+        order = [r for r in self.running if pending(r) == 1] + [r for r in self.running if pending(r) > 1]
         for req in order:
             if req.state != "running":
                 continue  # preempted a moment ago
             if budget <= 0:
                 break
-            n = min(req.pending, self.prefill_chunk, budget)
+            n = min(pending(req), self.prefill_chunk, budget)
             while not fits(req.id, req.committed, n):
                 if self.admission == "reserve":
                     raise AssertionError("page reservation was violated")  # cannot happen by construction

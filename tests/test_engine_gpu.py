@@ -253,13 +253,18 @@ def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
                # portions of prompts beside decode tokens, launched ahead as well
                dict(cuda_graphs=False, lookahead=True, prefill_chunk=7, max_admit=1),
                dict(cuda_graphs=True, lookahead=True, prefill_chunk=5, max_step_tokens=9),
-               dict(cuda_graphs=False, lookahead=False, prefill_chunk=7, max_admit=1)):
+               dict(cuda_graphs=False, lookahead=False, prefill_chunk=7, max_admit=1),
+               # a queue: four requests through two slots, so that steps which admit somebody are launched ahead too
+               dict(cuda_graphs=True, lookahead=True, max_running=2), dict(cuda_graphs=False, lookahead=True, max_running=2, prefill_chunk=7),
+               dict(cuda_graphs=True, lookahead=False, max_running=2)):
         eng = engine(model, num_blocks=40, block_size=8, **kw)
         assert eng.generate(prompts, plist) == want, kw
         eng.cache.check()
         assert eng.cache.live == [] and all(f == 40 for f in eng.cache.free_pages()), kw
         if kw.get("lookahead") and not kw["cuda_graphs"]:
             assert eng.launched_ahead > 0, kw
+        if kw.get("lookahead") and kw.get("max_running") == 2:
+            assert eng.launched_ahead >= eng.steps - 4, kw   # nearly every step, those that admit the third and fourth included
 
 
 def test_a_step_launched_for_requests_that_are_gone_costs_no_call(tiny_folders):

@@ -231,3 +231,32 @@ def test_a_requests_uniforms_are_the_stream_of_single_draws():
     r = Request(0, [1], SamplingParams(seed=5))
     g = torch.Generator().manual_seed(5)
     assert [r.next_uniform() for _ in range(21)] == [float(torch.rand(1, generator=g)) for _ in range(21)]
+
+
+def test_a_batch_composed_while_a_step_is_in_flight_admits_and_takes_tokens_on_the_device():
+    """`next_batch(ahead=...)`: the requests whose next token the step in flight samples bring a placeholder with
+    the row to take it from, unless that token is their last; a waiting request that fits is admitted beside them;
+    a portion of a prompt goes on from where the step in flight leaves it.  Optimistic admission declines."""
+    s = Scheduler(cache(), max_admit=1, prefill_chunk=6)
+    a, b, c = req(0, 5, max_tokens=3), req(1, 9, max_tokens=4), req(2, 4, max_tokens=2)
+    for r in (a, b, c):
+        s.add(r)
+    run_step(s)                                        # a's prompt; a has one token now
+    first = s.next_batch()                             # a decodes, b's first portion
+    assert [(x.req.id, len(x.tokens), x.samples) for x in first] == [(0, 1, True), (1, 6, False)]
+    for sch in first:                                  # the step is launched: pages taken, positions committed, no token yet
+        s.cache.extend(sch.req.id, len(sch.tokens))
+        sch.req.committed += len(sch.tokens)
+    ahead = s.next_batch(ahead={id(a): 0})
+    assert [(x.req.id, len(x.tokens), x.samples, x.from_row) for x in ahead] == [(0, 1, True, 0), (1, 3, True, None), (2, 4, True, None)]
+    assert ahead[0].tokens == [0] and ahead[1].tokens == [7, 8, 9] and c.state == "running"
+    for sch in ahead:
+        s.cache.extend(sch.req.id, len(sch.tokens))
+        sch.req.committed += len(sch.tokens)
+    a.out_tokens.append(7)                             # the first step's token arrives: a has two of its three ...
+    # ... and the step in flight samples its last: the batch after it has no row for a; b and c, whose first tokens
+    # are in flight, go on with placeholders
+    after = s.next_batch(ahead={id(a): 0, id(b): 1, id(c): 2})
+    assert [(x.req.id, x.tokens, x.from_row) for x in after] == [(1, [0], 1), (2, [0], 2)]
+    s.cache.check()
+    assert Scheduler(cache(), admission="optimistic").next_batch(ahead={}) is None

@@ -218,6 +218,19 @@ def test_a_hundred_requests_decode_in_one_step_beside_two_portions(dtype, wide_f
     for r in seqs:
         runner.end(r)
     runner.manager.check()
+    if dtype != "bfloat16":
+        return
+    # The same steps again and again give the same bits.  Kernels overlap their predecessors' tails, so what runs
+    # beside what changes from run to run; a wait inside a kernel that only holds for the usual timing shows up here
+    # (the prefill attention once read its accumulator on a barrier parity two phases ahead, a few runs in a hundred).
+    for again in range(40):
+        runner = ModelRunner(model, num_blocks=700, block_size=16, max_requests=102)
+        for r in seqs:
+            runner.begin(r)
+        for lo in range(0, 100, 25):
+            runner.step([StepEntry(r, seqs[r][:-1]) for r in range(lo, lo + 25)])
+        runner.step([StepEntry(100, seqs[100][:100])])
+        assert np.array_equal(runner.step(entries).float().cpu().numpy(), out), f"run {again} differs from the first"
 
 
 # ---------------------------------------------------------------------------------------------------
