@@ -176,9 +176,9 @@ class DecodeGraphs:
     def launch(self, batch: list[Scheduled], uniforms: list[float], take: tuple[torch.Tensor, list[int]] | None = None,
                ) -> "InFlight":
         """Reserves pages, fills the bucket's description, copies it and replays the graph; does not
-        wait.  With `take` = (int32 device tensor, one row of it per request) the step's token ids are
-        tokens that an earlier step sampled and that the host has not seen: the step can be launched
-        before they have reached it."""
+        wait.  With `take` = (int32 device tensor, one row of it per request, or None for a request whose token the
+        host knows) the step's token ids are tokens that an earlier step sampled and that the host has not seen: the
+        step can be launched before they have reached it."""
         runner = self.runner
         m = runner.manager
         B = len(batch)
@@ -198,17 +198,23 @@ class DecodeGraphs:
         if self.timing is not None:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
+        n_take = 0
         if take is not None:
-            bk.ids_host[:B] = 0
-            hn[o["take_dst"]: o["take_dst"] + B] = np.arange(B, dtype=np.int32)
-            hn[o["take_src"]: o["take_src"] + B] = take[1]
+            # rows whose token an earlier step sampled and the host has not seen take it on the device; the others
+            # (a prompt's last token, known all along) bring theirs from the host
+            rows = [i for i, r in enumerate(take[1]) if r is not None]
+            n_take = len(rows)
+            bk.ids_host[:B] = torch.tensor([0 if take[1][i] is not None else s.tokens[0] for i, s in enumerate(batch)], dtype=torch.int32)
+            hn[o["take_dst"]: o["take_dst"] + n_take] = rows
+            hn[o["take_src"]: o["take_src"] + n_take] = [take[1][i] for i in rows]
         else:
             bk.ids_host[:B] = torch.tensor([s.tokens[0] for s in batch], dtype=torch.int32)
         bk.ids_dev.copy_(bk.ids_host, non_blocking=True)  # padding rows carry -1
         bk.dev.copy_(bk.host, non_blocking=True)
         bk.copied.record()
-        if take is not None:
-            ops.take_ids(bk.ids_dev, bk.dev[o["take_dst"]: o["take_dst"] + B], take[0], bk.dev[o["take_src"]: o["take_src"] + B])
+        if n_take:
+            ops.take_ids(bk.ids_dev, bk.dev[o["take_dst"]: o["take_dst"] + n_take], take[0],
+                         bk.dev[o["take_src"]: o["take_src"] + n_take])
         runner.h2d_bytes_last = (bk.total + bk.size) * 4
         runner.storage.zero_state_slots(m.take_fresh_slots())
         bk.graph.replay()

@@ -256,7 +256,10 @@ def test_a_step_launched_ahead_changes_nothing(tiny_folders, tmp_path):
                dict(cuda_graphs=False, lookahead=False, prefill_chunk=7, max_admit=1),
                # a queue: four requests through two slots, so that steps which admit somebody are launched ahead too
                dict(cuda_graphs=True, lookahead=True, max_running=2), dict(cuda_graphs=False, lookahead=True, max_running=2, prefill_chunk=7),
-               dict(cuda_graphs=True, lookahead=False, max_running=2)):
+               dict(cuda_graphs=True, lookahead=False, max_running=2),
+               # portions of one token: a prompt's last token, which the host knows, shares a graph step launched ahead with
+               # decode tokens that are still on the device
+               dict(cuda_graphs=True, lookahead=True, prefill_chunk=1, max_admit=1)):
         eng = engine(model, num_blocks=40, block_size=8, **kw)
         assert eng.generate(prompts, plist) == want, kw
         eng.cache.check()

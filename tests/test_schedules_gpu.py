@@ -570,3 +570,28 @@ def test_layers_with_a_window_beside_layers_with_all_keys_through_the_engine(dty
             ids = list(prompt) + req.out_tokens
             want = plain_logits(ids[:-1])[len(prompt) - 1:].numpy()
             check_rows(torch.stack(req.step_logits).numpy(), want, dt, f"windowed layers, {dtype}, graphs={graphs}, request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_at_real_widths_keeps_every_logit(dtype, wide_folders):
+    """Optimistic admission on a pool that is far too small (dozens of preemptions), heads of 64 at real widths,
+    graphs on: requests are dropped and recomputed from their prompt plus what they had emitted.  Every step's
+    logits against the plain implementation over the request's own tokens; in float32 the tokens are those of an
+    engine with room for everybody."""
+    dt = DTYPES[dtype]
+    folder = wide_folders["wide64"]
+    vocab = WIDE["wide64"].vocab_size
+    cfg, w = plain_on_gpu(folder)
+    model = load(folder, dt)
+    prompts = [random_ids(10 + (53 * i) % 200, vocab, seed=300 + i) for i in range(10)]
+    plist = [params(max_tokens=16 + (i * 7) % 20) for i in range(10)]
+    eng = engine(model, num_blocks=24, block_size=16, admission="optimistic", prefill_chunk=64, record_logits=True)
+    reqs = [eng.add(p, s) for p, s in zip(prompts, plist)]
+    while eng.sched.has_work:
+        eng.step()
+        eng.cache.check()
+    assert eng.sched.preempted_total >= 10 and eng.cache.free_pages() == [24] and eng.cache.live == []
+    check_teacher_forced(reqs, prompts, cfg, w, dt, f"preemption at real widths, {dtype}")
+    if dtype == "float32":
+        roomy = engine(model, num_blocks=400, block_size=16, cuda_graphs=False, lookahead=False)
+        assert roomy.generate(prompts, plist) == [r.out_tokens for r in reqs]
