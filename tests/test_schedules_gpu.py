@@ -595,3 +595,59 @@ def test_preemption_at_real_widths_keeps_every_logit(dtype, wide_folders):
     if dtype == "float32":
         roomy = engine(model, num_blocks=400, block_size=16, cuda_graphs=False, lookahead=False)
         assert roomy.generate(prompts, plist) == [r.out_tokens for r in reqs]
+
+
+# ---------------------------------------------------------------------------------------------------
+# random schedules
+# ---------------------------------------------------------------------------------------------------
+def test_random_engine_options_and_arrivals_give_the_plain_tokens(tiny_folders):
+    """Sixty random combinations of everything the scheduler can be told - pool size down to what the largest request
+    needs, page-sized to whole-prompt portions, a token budget down to one, one to eight live requests, both
+    admission policies, graphs, launching ahead, the head in chunks, requests that arrive later - on the three tiny
+    models in float32, where the tokens must be the plain implementation's whatever the schedule."""
+    import random
+
+    models = {n: load(tiny_folders[n], torch.float32) for n in TINY}
+    plains = {n: plain.read_folder(tiny_folders[n]) for n in TINY}
+    known: dict[tuple, list[int]] = {}
+
+    def greedy(name, prompt, n):
+        key = (name, tuple(prompt))
+        if key not in known or len(known[key]) < n:
+            known[key] = plain.plain_greedy(*plains[name], prompt, n)[0]
+        return known[key][:n]
+
+    for it in range(60):
+        rng = random.Random(7000 + it)
+        name = rng.choice(list(TINY))
+        cfg, page = TINY[name]["config"], TINY[name]["page"]
+        max_pos = cfg.max_position_embeddings
+        reqs = []
+        for _ in range(rng.randint(1, 9)):
+            plen = rng.choice([1, 2, 3, rng.randint(1, 40), rng.randint(1, min(120, max_pos - 20))])
+            reqs.append((random_ids(plen, cfg.vocab_size, seed=rng.randint(0, 50)), rng.randint(1, min(14, max_pos - plen))))
+        need = max(-(-(len(p) + n) // page) for p, n in reqs)
+        kw = dict(num_blocks=rng.choice([need, need + 1, need + rng.randint(0, 10), 200]), block_size=page,
+                  cuda_graphs=rng.random() < 0.6, lookahead=rng.random() < 0.7, max_admit=rng.choice([1, 2, 32]),
+                  max_running=rng.choice([None, 1, 2, 3, 8]), prefill_chunk=rng.choice([1, 2, 5, 16, 2048]),
+                  max_step_tokens=rng.choice([1, 3, 9, 40, 8192]), admission=rng.choice(["reserve", "optimistic"]),
+                  head_chunk=rng.choice([1, 3, 256]), capture_at_start=rng.random() < 0.3)
+        eng = engine(models[name], **kw)
+        rs = [eng.add(p, params(max_tokens=n)) for p, n in reqs]
+        late = []
+        if rng.random() < 0.5 and len(rs) > 2:  # the last two arrive after three steps
+            late = rs[-2:]
+            for r in late:
+                eng.sched.waiting.remove(r)
+        steps = 0
+        while eng.sched.has_work or late:
+            if late and (steps >= 3 or not eng.sched.has_work):
+                for r in late:
+                    eng.sched.add(r)
+                late = []
+            eng.step()
+            steps += 1
+            eng.cache.check()
+            assert steps < 5000, (it, kw)
+        assert [r.out_tokens for r in rs] == [greedy(name, p, n) for p, n in reqs], (it, name, kw, [(len(p), n) for p, n in reqs])
+        assert eng.cache.live == [] and all(f == kw["num_blocks"] for f in eng.cache.free_pages()), (it, kw)
