@@ -651,3 +651,46 @@ def test_random_engine_options_and_arrivals_give_the_plain_tokens(tiny_folders):
             assert steps < 5000, (it, kw)
         assert [r.out_tokens for r in rs] == [greedy(name, p, n) for p, n in reqs], (it, name, kw, [(len(p), n) for p, n in reqs])
         assert eng.cache.live == [] and all(f == kw["num_blocks"] for f in eng.cache.free_pages()), (it, kw)
+
+
+@pytest.mark.parametrize("name", ["wide64", "wide128"])
+def test_random_cuts_at_real_widths(name, wide_folders):
+    """Fifteen random traces per model in bfloat16: one to six requests of 1 to 700 tokens, every step a random choice of
+    who takes part and of portion sizes that sit on and beside every tile edge of the kernels (1, 2, 3, 15-17, 31-33, 63-65,
+    127-129, 255-257, 300), pages of 8 to 64, pools with two pages to spare; the logits of every position against the
+    plain implementation."""
+    import random
+
+    from nanospec_b200.engine import ModelRunner, StepEntry
+
+    sizes = [1, 1, 1, 2, 3, 15, 16, 17, 31, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 300]
+    vocab = WIDE[name].vocab_size
+    cfg, w = plain_on_gpu(wide_folders[name])
+    model = load(wide_folders[name], torch.bfloat16)
+    for it in range(15):
+        rng = random.Random(4200 + it)
+        lens = [rng.choice([1, 2, 5, 64, 65, 129, rng.randint(1, 400), rng.randint(200, 700)]) for _ in range(rng.randint(1, 6))]
+        seqs = {r: random_ids(n, vocab, seed=rng.randint(0, 10 ** 6)) for r, n in enumerate(lens)}
+        page = rng.choice([8, 16, 32, 64])
+        runner = ModelRunner(model, num_blocks=sum(-(-n // page) for n in lens) + 2, block_size=page, max_requests=8)
+        for r in seqs:
+            runner.begin(r)
+        pos = {r: 0 for r in seqs}
+        got = {r: [] for r in seqs}
+        first = True
+        while any(pos[r] < lens[r] for r in seqs):
+            entries = [(r, pos[r], min(rng.choice(sizes), lens[r] - pos[r])) for r in seqs
+                       if pos[r] < lens[r] and (first or rng.random() >= 0.2)]
+            if not entries:
+                continue
+            first = False
+            out = runner.step([StepEntry(r, seqs[r][a: a + n], list(range(n))) for r, a, n in entries]).float().cpu().numpy()
+            row = 0
+            for r, a, n in entries:
+                got[r].append(out[row: row + n])
+                row += n
+                pos[r] = a + n
+        runner.manager.check()
+        for r, ids in seqs.items():
+            check_rows(np.concatenate(got[r]), plain.plain_forward(cfg, w, ids).cpu().numpy(), torch.bfloat16,
+                       f"{name}, trace {it}, pages of {page}, request {r} of {lens[r]} tokens")
