@@ -180,7 +180,9 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
 
         unsigned tau_p = 0u;
         if (p_keep < 1.f) {
-            // smallest key t with mass(key > t) <= top_p; kept by top-p = {key >= t}
+            // smallest key t with mass(key > t) <= top_p; kept by top-p = {key >= t}.  Logits that tie exactly at t are
+            // all kept: the reference's descending sort (spec/sampling.py:29-33) keeps whichever of them it happens to
+            // place first, which no order of the vocabulary decides
             unsigned lo = 0u;  // bitwise descent: build the smallest t for which the predicate holds
             for (int bit = 31; bit >= 0; --bit) {
                 // candidate with this bit cleared and all lower bits set is the largest value in the lower half
