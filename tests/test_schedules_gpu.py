@@ -694,3 +694,50 @@ def test_random_cuts_at_real_widths(name, wide_folders):
         for r, ids in seqs.items():
             check_rows(np.concatenate(got[r]), plain.plain_forward(cfg, w, ids).cpu().numpy(), torch.bfloat16,
                        f"{name}, trace {it}, pages of {page}, request {r} of {lens[r]} tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,heads,kv", [(16, 6, 3), (48, 9, 3), (80, 4, 1), (96, 6, 2), (112, 3, 3), (64, 24, 2), (160, 2, 1), (256, 2, 2)])
+def test_whole_models_at_other_head_sizes(d, heads, kv, dtype, tmp_path):
+    """Head sizes in steps of 16 from 16 to 128 (the tensor-core attention kernels: a group of 12 query heads per kv head
+    among them), and 160 and 256 (the exact kernel), as whole two-layer models with widths that are no power of two:
+    random cuts with pages of 4 to 32, every position's logits against the plain implementation."""
+    import random
+
+    from nanospec_b200.config import Llama3RopeScaling, LlamaConfig
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.weights import write_random_model
+
+    cfg_t = LlamaConfig(vocab_size=503 + d, hidden_size=16 * ((heads * d // 2) // 16 + 3), intermediate_size=24 * (d // 8 + 5),
+                        num_hidden_layers=2, num_attention_heads=heads, num_key_value_heads=kv, head_dim=d, rms_norm_eps=1e-5,
+                        rope_theta=50000.0, max_position_embeddings=1024,
+                        rope_scaling=Llama3RopeScaling(4.0, 1.0, 4.0, 128) if d % 32 else None)
+    write_random_model(tmp_path, cfg_t, seed=4)
+    cfg, w = plain_on_gpu(tmp_path)
+    dt = DTYPES[dtype]
+    model = load(tmp_path, dt)
+    sizes = [1, 1, 2, 3, 15, 17, 33, 63, 64, 65, 127, 129, 200]
+    for it in range(3):
+        rng = random.Random(100 * d + it)
+        lens = [rng.choice([1, 2, 65, 129, rng.randint(1, 300), rng.randint(200, 600)]) for _ in range(rng.randint(1, 5))]
+        seqs = {r: random_ids(n, cfg_t.vocab_size, seed=rng.randint(0, 10 ** 6)) for r, n in enumerate(lens)}
+        page = rng.choice([4, 8, 16, 32])
+        runner = ModelRunner(model, num_blocks=sum(-(-n // page) for n in lens) + 2, block_size=page, max_requests=8)
+        for r in seqs:
+            runner.begin(r)
+        pos = {r: 0 for r in seqs}
+        got = {r: [] for r in seqs}
+        while any(pos[r] < lens[r] for r in seqs):
+            entries = [(r, pos[r], min(rng.choice(sizes), lens[r] - pos[r])) for r in seqs if pos[r] < lens[r] and rng.random() > 0.15]
+            if not entries:
+                continue
+            out = runner.step([StepEntry(r, seqs[r][a: a + n], list(range(n))) for r, a, n in entries]).float().cpu().numpy()
+            row = 0
+            for r, a, n in entries:
+                got[r].append(out[row: row + n])
+                row += n
+                pos[r] = a + n
+        runner.manager.check()
+        for r, ids in seqs.items():
+            check_rows(np.concatenate(got[r]), plain.plain_forward(cfg, w, ids).cpu().numpy(), dt,
+                       f"head size {d}, {heads} heads over {kv}, {dtype}, trace {it}, request {r}")
