@@ -158,8 +158,11 @@ class CacheManager:
 
     def __del__(self) -> None:
         h, self._h = getattr(self, "_h", None), None
-        if h:
-            self._lib.ns_cache_destroy(h)
+        try:
+            if h:
+                self._lib.ns_cache_destroy(h)
+        except Exception:  # the interpreter is shutting down and the library is gone: the process's memory goes with it
+            pass
 
     # ---- native calls ---------------------------------------------------------------------
     def _status(self, status: int) -> None:
