@@ -612,10 +612,45 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     if out.stride(1) != 1 or qkv.stride(1) != 1 or lane.k.dtype != qkv.dtype:
         raise KernelError("attention: row-major bfloat16 operands and a bfloat16 cache are needed")
     plan = _attention_plan(ctx)
+    both = bool(plan["n_decode"]) and plan["tiles"] is not None
+    if both and OVERLAP_MIXED_ATTENTION and not torch.cuda.is_current_stream_capturing():
+        # A step of decode tokens beside portions of prompts: the two kernels read the same cache and write different rows.
+        # The decode kernel goes to a side stream, so that its blocks fill the SMs which the prefill kernel's last,
+        # ragged round of blocks leaves idle instead of running before it on an otherwise empty GPU.
+        main = torch.cuda.current_stream()
+        side = _side_stream(qkv.device)
+        fork, join = _side_events(qkv.device)
+        fork.record(main)
+        side.wait_event(fork)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
+        with torch.cuda.stream(side):
+            attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
+                             plan["max_kv_len"])
+            join.record(side)
+        main.wait_event(join)
+        return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
                          plan["max_kv_len"])
     if plan["tiles"] is not None:
         attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
     return out
+
+
+OVERLAP_MIXED_ATTENTION = True
+_side: dict = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    st = _side.get((device, "stream"))
+    if st is None:
+        st = _side[(device, "stream")] = torch.cuda.Stream(device=device)
+    return st
+
+
+def _side_events(device: torch.device):
+    ev = _side.get((device, "events"))
+    if ev is None:
+        ev = _side[(device, "events")] = (torch.cuda.Event(), torch.cuda.Event())
+    return ev
 
