@@ -96,6 +96,17 @@ class Engine:
         ops.check_kernel_errors(self.device)
         return [r.out_tokens for r in reqs]
 
+    def update_weights(self, state: dict[str, torch.Tensor]) -> None:
+        """Copies new weights in place (checkpoint names; see `weights.update_weights`) and restarts every running
+        request from its prompt plus what it has emitted: its cache was computed by the old weights.  The reference's
+        `Engine.update_weights` (engine/engine.py:167-176 there).  A step that was launched ahead is dropped."""
+        from ..weights import update_weights
+
+        update_weights(self.model, state)
+        for req in list(self.sched.running):
+            self.sched.restart(req)
+        self._inflight = None
+
     def _emit(self, req: Request, info: TokenInfo) -> bool:
         """Appends the token; True when the request is done (the end token is kept in the output)."""
         req.out_tokens.append(info.token)

@@ -106,3 +106,52 @@ def load_model(folder: str | Path, device: str | torch.device = "cuda", dtype: t
     for f in files:
         f.close()
     return model
+
+
+def update_weights(model: DecoderModel, state: dict[str, torch.Tensor]) -> None:
+    """Replaces weights of a bound model in place (captured CUDA graphs and tensor maps keep pointing at the same
+    memory), the reference's `Engine.update_weights` (engine/engine.py:167-176 there) for this engine's packed
+    tensors.  `state`: checkpoint name -> tensor, any device and floating type.  A part that packs several
+    checkpoint tensors into one (q/k/v; gate/up) takes all of its tensors or none; names the model does not have and
+    wrong shapes are refused before anything is written."""
+    if not model.bound:
+        raise RuntimeError("the model has no weights bound")
+    specs = model.weight_specs()
+    unknown = sorted(set(state) - set(specs))
+    wrong = [(n, tuple(t.shape), specs[n].shape) for n, t in state.items() if n in specs and tuple(t.shape) != tuple(specs[n].shape)]
+    if unknown or wrong:
+        raise WeightError("update_weights", [], unknown, wrong)
+    for name, spec in specs.items():  # a head that shares the embedding's tensor is replaced through the embedding
+        if name in state and spec.alias is not None and spec.alias not in state:
+            head, table = getattr(model.head, "weight", None), getattr(model.embedding, "table", None)
+            if head is not None and table is not None and head.data_ptr() == table.data_ptr():
+                raise WeightError("update_weights", [], [], [], other=[f"{name} is tied to {spec.alias}: replace that tensor"])
+    jobs = []
+    for prefix, part in model._named_parts():
+        names = list(part.weight_specs())
+        given = [n for n in names if prefix + n in state]
+        if not given:
+            continue
+        if len(given) != len(names):
+            lacking = [prefix + n for n in names if n not in given]
+            raise WeightError("update_weights", lacking, [], [], other=[f"the tensors under {prefix} are packed together and are replaced together"])
+        jobs.append((prefix, part, names))
+    for prefix, part, names in jobs:
+        shadow = type(part)(part.spec, model.dtype, model.device)
+        shadow.bind({n: _cast(state[prefix + n], part.weight_specs()[n], model.dtype, model.device) for n in names})
+        _copy_tensors(part, shadow, prefix)
+
+
+def _copy_tensors(live, shadow, where: str) -> None:
+    """Every tensor that binding gave the shadow goes into the live part's tensor of the same name."""
+    from ..parts.base import Part
+
+    for attr, val in vars(shadow).items():
+        if isinstance(val, torch.Tensor):
+            target = getattr(live, attr, None)
+            if not isinstance(target, torch.Tensor) or target.shape != val.shape or target.dtype != val.dtype:
+                raise RuntimeError(f"{where}: the bound tensor {attr!r} cannot be replaced in place")
+            target.copy_(val)
+        elif isinstance(val, Part) and isinstance(getattr(live, attr, None), Part):
+            _copy_tensors(getattr(live, attr), val, where)
+

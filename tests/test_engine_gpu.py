@@ -304,3 +304,45 @@ def test_errors_are_loud(tiny_folders):
     cpu_model = __import__("nanospec_b200").load_model(tiny_folders["A"], device="cpu", dtype=torch.float32)
     with pytest.raises(RuntimeError, match="no CPU path"):
         engine(cpu_model)
+
+
+def test_weights_replaced_in_place_restart_the_running_requests(tiny_folders, tmp_path):
+    """`Engine.update_weights` (the reference's engine/engine.py:167-176): new weights are copied into the tensors the
+    kernels and the captured graphs point at, and every running request is recomputed from its prompt plus what it has
+    emitted.  After the swap the tokens are those of the plain implementation with the new weights over that longer prompt."""
+    from nanospec_b200.weights import WeightError, write_random_model
+
+    name = "B"
+    cfg_t = TINY[name]["config"]
+    other = tmp_path / "other"
+    write_random_model(other, cfg_t, seed=909)
+    cfg1, w1 = plain_model(name, tiny_folders[name])
+    cfg2, w2 = plain.read_folder(other)
+    new_state = {k: v for k, v in w2.items()}
+    prompts = [random_ids(n, cfg_t.vocab_size, seed=80 + n) for n in (7, 30, 2)]
+    for graphs in (True, False):
+        model = load(tiny_folders[name], torch.float32)
+        eng = engine(model, num_blocks=64, block_size=8, cuda_graphs=graphs)
+        reqs = [eng.add(p, params(max_tokens=12)) for p in prompts]
+        for _ in range(5):
+            eng.step()
+        before = [list(r.out_tokens) for r in reqs]
+        assert all(0 < len(b) < 12 for b in before) and eng._inflight is not None
+        for p, b in zip(prompts, before):
+            assert b == plain.plain_greedy(cfg1, w1, p, len(b))[0]
+        eng.update_weights(new_state)
+        assert eng._inflight is None and [r.state for r in reqs] == ["waiting"] * 3
+        while eng.sched.has_work:
+            eng.step()
+        for p, b, r in zip(prompts, before, reqs):
+            assert r.out_tokens[: len(b)] == b
+            assert r.out_tokens[len(b):] == plain.plain_greedy(cfg2, w2, p + b, 12 - len(b))[0], graphs
+        eng.cache.check()
+        # a part's packed tensors go together; unknown names and wrong shapes are refused before anything is written
+        with pytest.raises(WeightError, match="replaced together"):
+            eng.update_weights({"model.layers.0.self_attn.q_proj.weight": w2["model.layers.0.self_attn.q_proj.weight"]})
+        with pytest.raises(WeightError, match="unexpected"):
+            eng.update_weights({"model.layers.9.mlp.down_proj.weight": w2["model.layers.0.mlp.down_proj.weight"]})
+        with pytest.raises(WeightError, match="wrong shape"):
+            eng.update_weights({"model.norm.weight": torch.ones(3)})
+        eng.update_weights({"model.norm.weight": w1["model.norm.weight"]})  # a part alone

@@ -741,3 +741,21 @@ def test_whole_models_at_other_head_sizes(d, heads, kv, dtype, tmp_path):
         for r, ids in seqs.items():
             check_rows(np.concatenate(got[r]), plain.plain_forward(cfg, w, ids).cpu().numpy(), dt,
                        f"head size {d}, {heads} heads over {kv}, {dtype}, trace {it}, request {r}")
+
+
+def test_weights_replaced_in_place_at_real_widths(wide_folders, tmp_path):
+    """The packed tensors of the fused kernels (q/k/v in one matrix, gate and up rows alternating in runs of 64, a head
+    tied to the embedding) are rebuilt from checkpoint tensors and copied in place: an engine whose weights were
+    replaced gives, through the graphs it captured before, the tokens of an engine loaded from the other folder."""
+    from nanospec_b200.weights import write_random_model
+
+    write_random_model(tmp_path, WIDE["wide64"], seed=77)
+    _, w2 = plain.read_folder(tmp_path)
+    vocab = WIDE["wide64"].vocab_size
+    prompts = [random_ids(n, vocab, seed=640 + n) for n in (9, 70, 33)]
+    swapped = engine(load(wide_folders["wide64"], torch.bfloat16), num_blocks=64, block_size=16)
+    first = swapped.generate(prompts, params(max_tokens=6))
+    swapped.update_weights({k: v for k, v in w2.items() if k != "lm_head.weight"})  # the head follows the embedding
+    fresh = engine(load(tmp_path, torch.bfloat16), num_blocks=64, block_size=16)
+    want = fresh.generate(prompts, params(max_tokens=10))
+    assert swapped.generate(prompts, params(max_tokens=10)) == want and [w[:6] for w in want] != first
