@@ -11,10 +11,14 @@ norm can feed a sink and the part after it takes row-scaled input (`Part.feeds_n
 norm's input in its epilogue, and the product after it applies the norm's scale.  `follow` is the
 block that runs next (or None): its first norm is the one after this block's feed-forward.
 
-Interface of a block part:
-    parts() -> dict of slot name -> Part           (for weight naming)
-    forward(resid, pending, ctx, lane, writes, follow=None) -> (resid, pending)
-    input_norm_sink(resid, ctx) -> ops.NormSink or None   (optional; None: the block's first norm cannot be folded)
+Interface of a block part (built from a whole `LayerSpec`):
+    mixer                                          the block's mixer part: the model asks it for the lane's cache and state needs
+    parts() -> dict of slot name -> Part           (for weight naming: `LayerSpec.names` maps each slot to its sub-prefix)
+    forward(resid, pending, ctx, lane, writes) -> (resid, pending)
+    takes_follow = True                            (optional) forward() also accepts `follow=`, the block that runs next
+    input_norm_sink(resid, ctx) -> ops.NormSink or None   (optional; None or absent: the block's first norm cannot be folded)
+The built-in mixers and feed-forwards return their result in the step's "branch" buffer: an arrangement that needs
+two branch outputs at once copies the first before it runs the second.
 """
 
 from __future__ import annotations

@@ -5,13 +5,15 @@ eps inside the root, the gain applied as is (not 1 + gain).  Here the statistics
 and the gain product are all float32 and the result is rounded once to the compute dtype.
 
 Interface of a norm part:
-    add_norm(resid, pending, ctx, rows=None) -> normed
-        resid   [N, H] float32, updated in place with `pending` when that is given
-        pending [N, H] compute dtype or None: a branch output not yet added to the stream
-        rows    int32 device tensor or None: only these rows are produced (resid untouched)
-    sink(resid, ctx) -> ops.NormSink    what a product needs to fold this norm and the sum before it
-                                        into its epilogue; `add_norm` hands the product's
-                                        `ops.RowScaled` result on unchanged
+    add_norm(resid, pending, ctx, rows=None, out_name="normed") -> normed
+        resid    [N, H] float32, updated in place with `pending` when that is given
+        pending  [N, H] compute dtype or None: a branch output not yet added to the stream
+        rows     int32 device tensor or None: only these rows are produced (resid untouched)
+        out_name the step buffer (`ctx.buffer(out_name, H, rows=...)`) that takes the result
+    sink(resid, ctx) -> ops.NormSink    (optional) what a product needs to fold this norm and the sum
+                                        before it into its epilogue; `add_norm` hands the product's
+                                        `ops.RowScaled` result on unchanged.  A norm without `sink`
+                                        is never folded.
 """
 
 from __future__ import annotations

@@ -483,3 +483,138 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
         want, choice = plain_logits(ids)
         assert len(set(choice.tolist())) > 1  # the router really sends tokens to different experts
         torch.testing.assert_close(torch.cat(got[r]), want, rtol=3e-5, atol=3e-6)
+
+
+def test_toy_norm_and_toy_block_arrangement(tmp_path):
+    """The last two kinds of part, defined here and registered from outside the package: a norm that centres
+    its input and has a bias (it cannot be folded into a product: it has no `sink`), and a block arrangement
+    that feeds one norm's output to the mixer and to the feed-forward side by side, x + mixer(n(x)) + ff(n(x)).
+    A model whose first layer is that block, whose second layer is the usual one and whose final norm is the toy
+    norm is written, loaded, stepped in portions and generated from through graphs, against a plain statement."""
+    import dataclasses
+
+    from nanospec_b200 import Engine, EngineConfig, SamplingParams
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.config import Architecture, LlamaConfig, PartSpec, register_architecture, registered_architectures
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.parts import Part, WeightSpec, build_part, register_part
+    from nanospec_b200.weights import load_model, write_random_model
+
+    @register_part("norm", "toy_centred")
+    class CentredNorm(Part):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.hidden, self.eps = spec["hidden"], spec["eps"]
+
+        def weight_specs(self):
+            return {"weight": WeightSpec((self.hidden,), rule="float32", init="gain"),
+                    "bias": WeightSpec((self.hidden,), rule="float32", std=0.1)}
+
+        def bind(self, tensors):
+            self.w = tensors
+
+        def add_norm(self, resid, pending, ctx, rows=None, out_name="normed"):
+            if rows is None:
+                if pending is not None:
+                    resid += pending.float()          # the stream takes the branch, in place
+                x = resid
+            else:                                     # only these rows, the stream untouched
+                x = resid[rows.long()] + (pending[rows.long()].float() if pending is not None else 0.0)
+            x = x - x.mean(dim=-1, keepdim=True)
+            y = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + self.eps) * self.w["weight"] + self.w["bias"]
+            out = ctx.buffer(out_name, self.hidden, rows=x.shape[0])
+            out.copy_(y)
+            return out
+
+    @register_part("block", "toy_side_by_side")
+    class SideBySide:
+        def __init__(self, layer, dtype, device):
+            self.mixer = build_part("mixer", layer.mixer, dtype, device)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device)
+            self.norm = build_part("norm", layer.norm, dtype, device)
+            self.hidden = layer.norm["hidden"]
+
+        def parts(self):
+            return {"norm": self.norm, "mixer": self.mixer, "feed_forward": self.feed_forward}
+
+        def forward(self, resid, pending, ctx, lane, writes=True):
+            x = self.norm.add_norm(resid, pending, ctx)
+            kept = ctx.buffer("toy_kept_branch", self.hidden)
+            kept.copy_(self.mixer.forward(x, ctx, lane, writes))  # the feed-forward's result takes the same buffer
+            out = self.feed_forward.forward(x, ctx)
+            out += kept
+            return resid, out
+
+    heads, kvh, d, hidden, inter, eps = 3, 1, 32, 72, 88, 3e-4
+    toy_norm = PartSpec("toy_centred", {"hidden": hidden, "eps": eps})
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        l0 = dataclasses.replace(r.layers[0], block="toy_side_by_side", norm=toy_norm,
+                                 names={"norm": "ln.", "mixer": "self_attn.", "feed_forward": "mlp."})
+        return dataclasses.replace(r, architecture="ToySideBySideForCausalLM", layers=(l0, r.layers[1]), final_norm=toy_norm)
+
+    if "ToySideBySideForCausalLM" not in registered_architectures():
+        register_architecture(Architecture("ToySideBySideForCausalLM", "toy-side-test", LlamaConfig.from_hf, recipe))
+    cfg = LlamaConfig(vocab_size=150, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=2, num_attention_heads=heads,
+                      num_key_value_heads=kvh, head_dim=d, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=128)
+    hf = cfg.to_hf()
+    hf["architectures"] = ["ToySideBySideForCausalLM"]
+    write_random_model(tmp_path, hf, seed=12)
+    pcfg, w = plain.read_folder(tmp_path)
+    assert "model.layers.0.ln.bias" in w and "model.norm.bias" in w and "model.layers.0.input_layernorm.weight" not in w
+    inv_freq = plain.plain_inv_freq(d, 10000.0, None)
+    shape = {"heads": heads, "kv_heads": kvh, "head_dim": d}
+
+    def centred(x, p):
+        x = x - x.mean(dim=-1, keepdim=True)
+        return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w[p + "weight"] + w[p + "bias"]
+
+    def plain_logits(ids):
+        positions = torch.arange(len(ids))
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)].float()
+        h = centred(x, "model.layers.0.ln.")
+        x = x + plain.plain_attention_block(h, w, "model.layers.0.self_attn.", shape, positions, inv_freq) \
+            + plain.plain_mlp(h, w, "model.layers.0.mlp.")
+        x = plain.plain_layer(x, w, 1, pcfg, positions, inv_freq)
+        return centred(x, "model.norm.") @ w["lm_head.weight"].float().T
+
+    model = load_model(tmp_path, device="cuda", dtype=torch.float32)
+    seqs = {0: random_ids(41, 150, seed=21), 1: random_ids(18, 150, seed=22)}
+    runner = ModelRunner(model, num_blocks=24, block_size=4, max_requests=2)
+    got = {r: [] for r in seqs}
+
+    def run(entries):
+        out = runner.step([StepEntry(r, seqs[r][a:b], list(range(b - a))) for r, a, b in entries])
+        row = 0
+        for r, a, b in entries:
+            got[r].append(out[row: row + b - a].float().cpu())
+            row += b - a
+
+    runner.begin(0), runner.begin(1)
+    run([(0, 0, 13), (1, 0, 2)])
+    run([(1, 2, 3), (0, 13, 15)])
+    run([(0, 15, 40), (1, 3, 18)])
+    run([(0, 40, 41)])
+    runner.end(0), runner.end(1)
+    runner.manager.check()
+    for r, ids in seqs.items():
+        torch.testing.assert_close(torch.cat(got[r]), plain_logits(ids), rtol=3e-5, atol=3e-6)
+    del runner
+
+    # through the entry point, decode steps replayed from graphs (the toy parts are torch operations on device
+    # tensors: they can be captured) and launched ahead, against eager steps and against the plain argmax
+    prompts = [seqs[0][:9], seqs[1][:4], seqs[0][5:30]]
+    outs = {}
+    for graphs in (True, False):
+        eng = Engine(model, EngineConfig(num_blocks=64, block_size=4, cuda_graphs=graphs, prefill_chunk=7, max_running=3))
+        outs[graphs] = eng.generate(prompts, SamplingParams(max_tokens=6))
+        assert not graphs or eng.graphs.replays >= 4
+    for graphs in (True, False):
+        for p, o in zip(prompts, outs[graphs]):
+            ids = list(p)
+            for t in o:
+                z = plain_logits(ids)[-1]
+                top = z.topk(2).values
+                assert t == int(z.argmax()) or float(top[0] - top[1]) < 1e-5
+                ids.append(t)
