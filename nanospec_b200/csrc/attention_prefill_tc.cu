@@ -22,7 +22,8 @@
 //
 // Every mbarrier wait is bounded (two seconds); a wait that runs out sets *error_flag and the
 // block winds down.  Other head sizes, page sizes other than 8/16/32/64 and windows
-// are served by the m16n8k16 kernel of attention_prefill.cu.
+// are served by the m16n8k16 kernel of attention_prefill.cu.  A second kernel below takes heads of 64 in groups
+// of an even size, two query heads to a block.
 #include "tcgen05_utils.cuh"
 
 namespace {
@@ -343,6 +344,269 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Head size 64, an even number of query heads per kv head: one block = 256 query tokens of TWO query heads
+// that share a kv head, i.e. four tiles of 128 rows on one stream of keys and values.  With heads of 64 the
+// products of a 64-key block need half the tensor-core time of heads of 128 while the softmax costs the
+// same, so the kernel above is bound by the exponentials and by the chain scores -> softmax -> P V of its two
+// tiles.  Four tiles put four softmax warps on every sub-partition, which keeps its exponential unit busy
+// while other warps wait, load or store; TMEM holds them with one buffer of scores per tile (4 x 64 columns
+// of S, with P over their first half, and 4 x 64 of O), so a tile's scores of block j+1 follow its P V of
+// block j, and the other three tiles fill the tensor core meanwhile.
+// The accumulator is up to date whenever a tile's scores arrive (they were issued after its last P V had
+// completed), so a rescale needs no barrier.
+constexpr int kTiles4 = 4;
+constexpr int kTc4Threads = 96 + kTiles4 * 128;
+constexpr int kSmem4 = kTiles4 * kBQ * 64 * 2 + kKvStages * 2 * kBK * 64 * 2 + 1024 + 512;
+
+__global__ void __launch_bounds__(kTc4Threads, 1)
+attention_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                             int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
+                             const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
+                             int page_size, float scale, int* __restrict__ error_flag) {
+    ns_pdl_launch_dependents();
+    constexpr int kD = 64;
+    constexpr int kQBytes = kBQ * kD * 2, kKBytes = kBK * kD * 2;
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t q_smem = base;                                   // [tile]
+    const uint32_t kv_smem = q_smem + kTiles4 * kQBytes;            // [stage][K | V]
+    const uint32_t bar0 = kv_smem + kKvStages * 2 * kKBytes;
+    // barriers: q_full, kv_full[stage], kv_empty[stage], then per tile s_full, s_free, p_ready, o_final
+    const uint32_t q_full = bar0;
+    auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kKvStages + s); };
+    auto tile_bar = [&](int tt, int which) { return bar0 + 8u * (1 + 2 * kKvStages + tt * 4 + which); };
+    auto s_full = [&](int tt) { return tile_bar(tt, 0); };   // the scores of the tile's next block are in TMEM
+    auto s_free = [&](int tt) { return tile_bar(tt, 1); };   // the P V that read P (over the scores) has completed
+    auto p_ready = [&](int tt) { return tile_bar(tt, 2); };  // the 128 softmax threads have stored P
+    auto o_final = [&](int tt) { return tile_bar(tt, 3); };  // the P V of the tile's last block has completed
+    const uint32_t holder = bar0 + 8u * (1 + 2 * kKvStages + kTiles4 * 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int req = tiles[2 * blockIdx.y], q_off = tiles[2 * blockIdx.y + 1];
+    const int h0 = 2 * blockIdx.x;          // tiles 0, 1: head h0; tiles 2, 3: head h0 + 1 (the same kv head)
+    const int hk = h0 / (nq / nkv);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int tt = 0; tt < kTiles4; ++tt) {
+            mbar_init(s_full(tt), 1);
+            mbar_init(s_free(tt), 1);
+            mbar_init(p_ready(tt), 128);
+            mbar_init(o_final(tt), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) tmem_alloc(holder, kTmemColsTc);
+    ns_pdl_wait();  // everything below reads what earlier kernels wrote (q, the cache, the step's description)
+    const int tok0 = qo_indptr[req] + q_off;
+    const int rows_all = min(2 * kBQ, qo_indptr[req + 1] - tok0);
+    const int pos0 = positions[tok0];
+    // per row tile (tile & 1): its valid rows and the number of key blocks its last row sees (0 rows: idle)
+    int rows_t[2], nblk_t[2];
+    int n_blocks = 0;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        rows_t[t] = max(0, min(kBQ, rows_all - t * kBQ));
+        nblk_t[t] = rows_t[t] > 0 ? (pos0 + t * kBQ + rows_t[t] + kBK - 1) / kBK : 0;
+        n_blocks = max(n_blocks, nblk_t[t]);
+    }
+    const int* bt = block_table + (size_t)req * table_stride;
+    const int last_blk = (pos0 + rows_all - 1) / page_size;  // the last page that holds one of the keys seen here
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
+    auto tmem_s = [&](int tt) { return tmem_base + (uint32_t)(tt * 64); };
+    auto tmem_o = [&](int tt) { return tmem_base + 256u + (uint32_t)(tt * 64); };
+
+    if (warp == 0) {
+        // ---------------- loader ----------------
+        if (elect_one()) {
+            mbar_expect_tx(q_full, kTiles4 * kQBytes);
+            for (int tt = 0; tt < kTiles4; ++tt)  // rows past the step's tokens are zero-filled by TMA
+                tma_load_2d(q_smem + tt * kQBytes, &map_q, (h0 + (tt >> 1)) * kD, tok0 + (tt & 1) * kBQ, q_full);
+        }
+        const int pages_per_block = kBK / page_size;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int s = j % kKvStages;
+            if (!mbar_wait_warp(kv_empty(s), ((uint32_t)(j / kKvStages) & 1u) ^ 1u)) { if (lane == 0) atomicExch(error_flag, kErrAttnLoader); break; }
+            if (elect_one()) mbar_expect_tx(kv_full(s), 2 * kKBytes);
+            const uint32_t k_dst = kv_smem + s * 2 * kKBytes, v_dst = k_dst + kKBytes;
+            for (int i = 0; i < pages_per_block; ++i) {
+                // pages past the last key repeat the last page: finite values that the mask hides
+                const int blk = min(j * pages_per_block + i, last_blk);
+                const int row = (bt[blk] * nkv + hk) * page_size;
+                const uint32_t off = (uint32_t)(i * page_size) * 128u;
+                if (elect_one()) {
+                    tma_load_2d(k_dst + off, &map_k, 0, row, kv_full(s));
+                    tma_load_2d(v_dst + off, &map_v, 0, row, kv_full(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- issuer of S = Q K^T ----------------
+        constexpr uint32_t idesc_s = idesc_tc(kBK, false);
+        bool ok = mbar_wait_warp(q_full, 0);
+        for (int j = 0; ok && j < n_blocks; ++j) {
+            const int s = j % kKvStages;
+            ok = mbar_wait_warp(kv_full(s), (uint32_t)(j / kKvStages) & 1u);
+            const uint32_t k_src = kv_smem + s * 2 * kKBytes;
+            for (int tt = 0; ok && tt < kTiles4; ++tt) {
+                if (j >= nblk_t[tt & 1]) continue;
+                // the tile's one buffer holds P of block j-1 until the product that reads it has completed
+                if (j > 0) ok = mbar_wait_warp(s_free(tt), (uint32_t)(j - 1) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk)
+                    if (elect_one())
+                        umma_bf16(tmem_s(tt), smem_desc(q_smem + tt * kQBytes + kk * 32), smem_desc(k_src + kk * 32), idesc_s,
+                                  kk > 0 ? 1u : 0u);
+                if (elect_one()) umma_commit(s_full(tt));
+            }
+        }
+        if (!ok && lane == 0) atomicExch(error_flag, kErrAttnMma);
+    } else if (warp == 2) {
+        // ---------------- issuer of O += P V ----------------
+        constexpr uint32_t idesc_o = idesc_tc(kD, true);
+        bool ok = true;
+        for (int j = 0; ok && j < n_blocks; ++j) {
+            const int s = j % kKvStages;
+            const uint32_t v_src = kv_smem + s * 2 * kKBytes + kKBytes;
+            for (int tt = 0; ok && tt < kTiles4; ++tt) {
+                if (j >= nblk_t[tt & 1]) continue;
+                ok = mbar_wait_warp(p_ready(tt), (uint32_t)j & 1u);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; ++kk)  // 16 keys = 8 columns of bf16 pairs
+                    if (elect_one())
+                        umma_bf16_ts(tmem_o(tt), tmem_s(tt) + kk * 8, smem_desc_mn(v_src + kk * 16 * 128, kBK * 128, 1024),
+                                     idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                if (elect_one()) {
+                    umma_commit(s_free(tt));                                    // the buffer may take the scores of block j+1
+                    if (j == nblk_t[tt & 1] - 1) umma_commit(o_final(tt));      // the tile's accumulator is complete
+                }
+            }
+            // every tile has read the stage's values; its keys were read by the scores of block j
+            if (ok && elect_one()) umma_commit(kv_empty(s));
+        }
+        if (!ok && lane == 0) atomicExch(error_flag, kErrAttnMma);
+    } else {
+        // ---------------- softmax and output: one query row per thread, one warpgroup per tile ----------------
+        const int tt = (warp - 3) >> 2;                            // the tile this warpgroup serves
+        const int t = tt & 1;                                      // its rows: the first or the second 128 of the block
+        const int h = h0 + (tt >> 1);
+        const int quarter = warp & 3;                              // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;                       // TMEM lane = query row of the tile
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int rows = rows_t[t], my_blocks = nblk_t[t];
+        const int tile_pos0 = pos0 + t * kBQ;
+        const int pos_row = tile_pos0 + min(row, max(rows, 1) - 1);
+        const float sl = scale * kLog2eTc;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < my_blocks; ++j) {
+            ok = mbar_wait_warp(s_full(tt), (uint32_t)j & 1u);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sv[2][32];
+            tmem_ld32(tmem_s(tt) + lane_addr, sv[0]);
+            tmem_ld32(tmem_s(tt) + lane_addr + 32, sv[1]);
+            tmem_ld_wait();
+            const int key0 = j * kBK;
+            if (key0 + kBK - 1 > tile_pos0) {                       // some row of the tile does not see the whole block
+#pragma unroll
+                for (int c = 0; c < kBK; ++c)
+                    if (key0 + c > pos_row) sv[c >> 5][c & 31] = 0xff800000u;  // -inf
+            }
+            float mx8[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(sv[0][c]);
+#pragma unroll
+            for (int c = 8; c < kBK; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(sv[c >> 5][c & 31]));
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            // the reference point follows the maximum lazily, as in the kernel above
+            const float cand = mx * sl;
+            const bool jump = cand > m + 8.f;
+            const float m_new = jump ? cand : m;
+            const float corr = jump ? ex2(m - m_new) : 1.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // the weights of columns 2u and 2u+1 go, as a bf16 pair, where score u lay: it has been used by then
+#pragma unroll
+            for (int u = 0; u < kBK / 2; ++u) {
+                const int c = 2 * u;
+                const float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sl, -m_new));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sl, -m_new));
+                sum4[u & 3] += p0 + p1;
+                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                sv[0][u] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            tmem_st32(tmem_s(tt) + lane_addr, sv[0]);
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            if (j > 0 && __any_sync(0xffffffffu, jump)) {
+                // the accumulator holds blocks 0..j-1: this block's scores were issued after that product completed
+#pragma unroll 1
+                for (int c0 = 0; c0 < kD; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_o(tt) + lane_addr + c0, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_st32(tmem_o(tt) + lane_addr + c0, ov);
+                }
+            }
+            m = m_new;
+            tmem_st_wait();                                         // P (and a rescaled O) are in TMEM
+            tc_fence_before();
+            mbar_arrive(p_ready(tt));
+        }
+        if (ok && my_blocks > 0) ok = mbar_wait_warp(o_final(tt), 0);
+        if (!ok) {
+            if (lane == 0) atomicExch(error_flag, kErrAttnSoftmax);
+        } else if (my_blocks > 0) {
+            tc_fence_after();
+            const float inv = 1.f / l;
+            __nv_bfloat16* orow = out + (size_t)(tok0 + t * kBQ + row) * o_stride + (size_t)h * kD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o(tt) + lane_addr + c0, ov);
+                tmem_ld_wait();
+                if (row < rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u;
+                        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+                        for (int w = 0; w < 4; ++w)
+                            hp[w] = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * w]) * inv, __uint_as_float(ov[i + 2 * w + 1]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c0 + i) = u;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemColsTc);
+    }
+}
+
+bool ns_prefill_tc_two_tiles = false;  // tests and measurements: heads of 64 on the two-tile kernel as well
+
 template <int kD>
 int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache, long long n_pages,
                       const int* block_table, int table_stride, const int* positions, const int* qo_indptr, const int* tiles,
@@ -356,6 +620,17 @@ int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_c
     if (rc) return rc;
     rc = ns_make_map_bf16(&mv, v_cache, cache_rows, kD, kD, page_size, "ns_attention_prefill_tc");
     if (rc) return rc;
+    if (kD == 64 && (nq / nkv) % 2 == 0 && !ns_prefill_tc_two_tiles) {
+        static bool configured4 = false;
+        if (!configured4) {
+            NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem4));
+            configured4 = true;
+        }
+        NS_LAUNCH(attention_prefill_tc4_kernel, dim3(nq / 2, n_tiles), kTc4Threads, kSmem4, stream, mq, mk, mv, block_table,
+                  table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, error_flag);
+        NS_CHECK_LAUNCH("ns_attention_prefill_tc");
+        return NS_OK;
+    }
     static bool configured = false;
     if (!configured) {
         NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<kD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -370,6 +645,11 @@ int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_c
 }
 
 }  // namespace
+
+NS_API int ns_attention_prefill_tc_two_tiles(int on) {
+    ns_prefill_tc_two_tiles = on != 0;
+    return NS_OK;
+}
 
 // q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
 // lane's pages [n_pages, nkv, page_size, head_dim]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of

@@ -393,11 +393,13 @@ def test_cluster_decode_attention(nq, nkv, d, page, window):
             assert float(out[len(lens):].abs().sum()) == 0.0  # the prompt portion's rows are not touched
 
 
-@pytest.mark.parametrize("nq,nkv,page,d", [(8, 2, 16, 128), (4, 4, 8, 128), (6, 1, 32, 128), (32, 8, 64, 128), (8, 2, 16, 64), (6, 3, 8, 64)])
+@pytest.mark.parametrize("nq,nkv,page,d", [(8, 2, 16, 128), (4, 4, 8, 128), (6, 1, 32, 128), (32, 8, 64, 128), (8, 2, 16, 64), (6, 3, 8, 64),
+                                           (32, 8, 16, 64), (3, 3, 16, 64), (9, 3, 32, 64), (2, 1, 64, 64)])
 def test_tcgen05_prefill_attention(nq, nkv, page, d):
-    """Head sizes 64 and 128 take the tcgen05 kernel: prompts from 2 to 1,500 tokens, portions that continue a
+    """Head sizes 64 and 128 take the tcgen05 kernels: prompts from 2 to 1,500 tokens, portions that continue a
     request, tiles that end inside a page, a far key that every query must find - against the plain
-    attention and against the m16n8k16 kernel."""
+    attention and against the m16n8k16 kernel.  Heads of 64 in groups of an even size run two heads to a block
+    (four tiles); the same sizes are run once more on the kernel with two tiles that odd groups take."""
     requests = [(1500, 1500, 7), (129, 128, 3), (700, 2, 650), (333, 70, 2), (64, 64, 63), (257, 129, 128), (1000, 300, 640)]
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=5000 // page + 40, seed=page)
     outs = {}
@@ -416,3 +418,16 @@ def test_tcgen05_prefill_attention(nq, nkv, page, d):
         torch.testing.assert_close(outs[True][row: row + q_len].float().cpu().view(q_len, nq, d), full[start:], rtol=3e-2, atol=3e-2)
         row += q_len
     torch.testing.assert_close(outs[True].float(), outs[False].float(), rtol=3e-2, atol=3e-2)
+    if d == 64 and (nq // nkv) % 2 == 0:
+        from nanospec_b200.ops import lib
+        lib.call("ns_attention_prefill_tc_two_tiles", 1)
+        try:
+            ctx.extras = {}
+            out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+            ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+            torch.cuda.synchronize()
+            ops().check_kernel_errors()
+        finally:
+            lib.call("ns_attention_prefill_tc_two_tiles", 0)
+        # the same scores in the same blocks of 64 keys: only the lazy reference point may differ between the two
+        torch.testing.assert_close(out.float(), outs[True].float(), rtol=2e-2, atol=2e-2)
