@@ -605,13 +605,11 @@ attention_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __
     }
 }
 
-bool ns_prefill_tc_two_tiles = false;  // tests and measurements: heads of 64 on the two-tile kernel as well
-
 template <int kD>
 int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache, long long n_pages,
                       const int* block_table, int table_stride, const int* positions, const int* qo_indptr, const int* tiles,
-                      int n_tiles, void* out, int o_stride, int nq, int nkv, int page_size, float scale, int* error_flag,
-                      cudaStream_t stream) {
+                      int n_tiles, void* out, int o_stride, int nq, int nkv, int page_size, float scale, int heads_per_block,
+                      int* error_flag, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     int rc = ns_make_map_bf16(&mq, q, (unsigned long long)n_tokens, nq * kD, q_stride, kBQ, "ns_attention_prefill_tc");
     if (rc) return rc;
@@ -620,7 +618,7 @@ int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_c
     if (rc) return rc;
     rc = ns_make_map_bf16(&mv, v_cache, cache_rows, kD, kD, page_size, "ns_attention_prefill_tc");
     if (rc) return rc;
-    if (kD == 64 && (nq / nkv) % 2 == 0 && !ns_prefill_tc_two_tiles) {
+    if (kD == 64 && heads_per_block == 2) {
         static bool configured4 = false;
         if (!configured4) {
             NS_CUDA(cudaFuncSetAttribute(attention_prefill_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem4));
@@ -646,18 +644,16 @@ int launch_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_c
 
 }  // namespace
 
-NS_API int ns_attention_prefill_tc_two_tiles(int on) {
-    ns_prefill_tc_two_tiles = on != 0;
-    return NS_OK;
-}
-
 // q: the step's packed projection (bf16, row stride q_stride elements, n_tokens rows); k_cache, v_cache: one
 // lane's pages [n_pages, nkv, page_size, head_dim]; tiles: int32 [n_tiles, 2] = (request, offset among its tokens of
 // this step, a multiple of 256).  Head sizes 64 and 128; page sizes 8, 16, 32, 64; out rows 16-byte aligned.
+// heads_per_block: 1, or 2 for heads of 64 in groups of an even size (two query heads of a kv head share a block and
+// its stream of keys and values: worth it once there are more blocks than SMs).
 NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
                                    long long n_pages, const int* block_table, int table_stride, const int* positions,
                                    const int* qo_indptr, const int* tiles, int n_tiles, void* out, int o_stride, int nq,
-                                   int nkv, int d, int page_size, float scale, int* error_flag, cudaStream_t stream) {
+                                   int nkv, int d, int page_size, float scale, int heads_per_block, int* error_flag,
+                                   cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
     if (d != 64 && d != 128) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: head_dim=%d (64 or 128)", d);
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
@@ -666,10 +662,13 @@ NS_API int ns_attention_prefill_tc(const void* q, int q_stride, int n_tokens, co
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: %d heads over %d kv heads, %d tiles", nq, nkv, n_tiles);
     if (q_stride % 8 || o_stride % 8 || ((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill_tc: rows must be 16-byte aligned");
+    if (heads_per_block != 1 && !(heads_per_block == 2 && d == 64 && (nq / nkv) % 2 == 0))
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: heads_per_block=%d (1, or 2 with heads of 64 in groups of an even size)", heads_per_block);
     if (!error_flag) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill_tc: no error flag");
     if (d == 64)
         return launch_prefill_tc<64>(q, q_stride, n_tokens, k_cache, v_cache, n_pages, block_table, table_stride, positions,
-                                     qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, error_flag, stream);
+                                     qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, heads_per_block, error_flag, stream);
     return launch_prefill_tc<128>(q, q_stride, n_tokens, k_cache, v_cache, n_pages, block_table, table_stride, positions,
-                                  qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, error_flag, stream);
+                                  qo_indptr, tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, heads_per_block, error_flag,
+                                  stream);
 }

@@ -555,6 +555,9 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
              n_splits, _stream())
 
 
+PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
+
+
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                       window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
@@ -562,11 +565,15 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
     if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+        # heads of 64: two query heads of a kv head to a block (four softmax warps per sub-partition keep the exponential
+        # unit busier and the keys are read once for both) - once one head to a block would give more blocks than SMs
+        two_heads = head_dim == 64 and (nq // nkv) % 2 == 0 and PREFILL_TWO_HEADS != "never" and (
+            PREFILL_TWO_HEADS == "always" or nq * tiles_tc.shape[0] > sm_count())
         lib.call("ns_attention_prefill_tc", qkv.data_ptr(), qkv.stride(0), qkv.shape[0], lane.k.data_ptr(),
                  lane.v.data_ptr(), lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0),
                  ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), tiles_tc.data_ptr(), tiles_tc.shape[0], out.data_ptr(),
-                 out.stride(0), nq, nkv, head_dim, lane.page_size, float(scale), _tc(qkv.device).error.data_ptr(),
-                 _stream())
+                 out.stride(0), nq, nkv, head_dim, lane.page_size, float(scale), 2 if two_heads else 1,
+                 _tc(qkv.device).error.data_ptr(), _stream())
         return
     lib.call("ns_attention_prefill", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),

@@ -402,32 +402,30 @@ def test_tcgen05_prefill_attention(nq, nkv, page, d):
     (four tiles); the same sizes are run once more on the kernel with two tiles that odd groups take."""
     requests = [(1500, 1500, 7), (129, 128, 3), (700, 2, 650), (333, 70, 2), (64, 64, 63), (257, 129, 128), (1000, 300, 640)]
     ctx, lane, qkv, want = _step(requests, nq, nkv, d, page, n_pages=5000 // page + 40, seed=page)
+    two_heads = d == 64 and (nq // nkv) % 2 == 0
     outs = {}
-    for tc in (True, False):
-        ops().USE_TCGEN05_ATTENTION = tc
-        ctx.extras = {}
-        out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
-        ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
-        torch.cuda.synchronize()
-        ops().check_kernel_errors()
-        outs[tc] = out
-    ops().USE_TCGEN05_ATTENTION = True
-    row = 0
-    for (S, q_len, _), (q, k, v, start) in zip(requests, want):
-        full = plain.plain_attention(q, k, v)
-        torch.testing.assert_close(outs[True][row: row + q_len].float().cpu().view(q_len, nq, d), full[start:], rtol=3e-2, atol=3e-2)
-        row += q_len
-    torch.testing.assert_close(outs[True].float(), outs[False].float(), rtol=3e-2, atol=3e-2)
-    if d == 64 and (nq // nkv) % 2 == 0:
-        from nanospec_b200.ops import lib
-        lib.call("ns_attention_prefill_tc_two_tiles", 1)
-        try:
+    try:
+        for tc in (True, False, "one head to a block"):
+            if tc == "one head to a block" and not two_heads:
+                continue
+            ops().USE_TCGEN05_ATTENTION = bool(tc)
+            ops().PREFILL_TWO_HEADS = "never" if tc == "one head to a block" else "always"
             ctx.extras = {}
             out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
             ops().attention(qkv, lane, ctx, out, nq, nkv, d, 1.0 / math.sqrt(d), 0)
             torch.cuda.synchronize()
             ops().check_kernel_errors()
-        finally:
-            lib.call("ns_attention_prefill_tc_two_tiles", 0)
+            outs[tc] = out
+    finally:
+        ops().USE_TCGEN05_ATTENTION = True
+        ops().PREFILL_TWO_HEADS = "auto"
+    row = 0
+    for (S, q_len, _), (q, k, v, start) in zip(requests, want):
+        full = plain.plain_attention(q, k, v)
+        for tc in outs:
+            torch.testing.assert_close(outs[tc][row: row + q_len].float().cpu().view(q_len, nq, d), full[start:], rtol=3e-2, atol=3e-2)
+        row += q_len
+    torch.testing.assert_close(outs[True].float(), outs[False].float(), rtol=3e-2, atol=3e-2)
+    if two_heads:
         # the same scores in the same blocks of 64 keys: only the lazy reference point may differ between the two
-        torch.testing.assert_close(out.float(), outs[True].float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(outs["one head to a block"].float(), outs[True].float(), rtol=2e-2, atol=2e-2)

@@ -203,6 +203,19 @@ def test_replay_with_heads_of_64(dtype, wide_folders, tmp_path):
     for cut, steps in cuts.items():
         results = run_trace(folder, dtype, steps, peak_tokens(steps), tmp_path / cut, block_size=16, vocab=vocab)
         check(collect(steps, results, seqs), want, dtype, f"heads of 64, {dtype}, {cut}")
+    if dtype == "bfloat16":
+        # Portions this short make fewer blocks than the GPU has SMs and take the prefill kernel with one query head to
+        # a block; once more with two heads to a block (what long prompts take), in this process
+        from nanospec_b200 import ops
+        model = load(folder, torch.bfloat16)
+        ops.PREFILL_TWO_HEADS = "always"
+        try:
+            for cut in ("whole", "mixed"):
+                steps = cuts[cut]
+                results, _, _ = replay_in_process(model, steps, -(-peak_tokens(steps) // 16), 16)
+                check(collect(steps, results, seqs), want, dtype, f"heads of 64, two heads to a block, {cut}")
+        finally:
+            ops.PREFILL_TWO_HEADS = "auto"
 
 
 # ---------------------------------------------------------------------------------------------------
