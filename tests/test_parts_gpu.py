@@ -618,3 +618,102 @@ def test_toy_norm_and_toy_block_arrangement(tmp_path):
                 top = z.topk(2).values
                 assert t == int(z.argmax()) or float(top[0] - top[1]) < 1e-5
                 ids.append(t)
+
+
+def test_toy_embedding_and_toy_head(tmp_path):
+    """The two remaining slots: an embedding that scales its rows by sqrt(hidden) and adds a learned offset, and a head
+    with a bias whose logits are soft-capped, both defined here.  Through the runner in portions and through
+    `Engine.generate` with graphs (head and sampling are inside the graph), against a plain statement."""
+    import dataclasses
+
+    from nanospec_b200 import Engine, EngineConfig, SamplingParams, ops
+    from nanospec_b200.architectures.llama import llama_recipe
+    from nanospec_b200.config import Architecture, LlamaConfig, PartSpec, register_architecture, registered_architectures
+    from nanospec_b200.engine import ModelRunner, StepEntry
+    from nanospec_b200.parts import Part, WeightSpec, register_part
+    from nanospec_b200.weights import load_model, write_random_model
+
+    vocab, hidden, cap = 130, 64, 3.0
+
+    @register_part("embedding", "toy_scaled")
+    class ScaledEmbedding(Part):
+        def weight_specs(self):
+            return {"weight": WeightSpec((vocab, hidden), std=0.05), "offset": WeightSpec((hidden,), rule="float32", std=0.1)}
+
+        def bind(self, tensors):
+            self.w = tensors
+
+        def forward(self, ctx):
+            resid = ops.embed(self.w["weight"], ctx.token_ids, ctx.buffer("resid", hidden, torch.float32))
+            resid.mul_(math.sqrt(hidden)).add_(self.w["offset"])
+            return resid
+
+    @register_part("head", "toy_soft_capped")
+    class SoftCappedHead(Part):
+        def weight_specs(self):
+            return {"weight": WeightSpec((vocab, hidden), std=0.3), "bias": WeightSpec((vocab,), rule="float32", std=0.5)}
+
+        def bind(self, tensors):
+            self.w = tensors
+
+        def forward(self, h, out=None):
+            z = ops.linear(h, self.w["weight"], torch.empty((h.shape[0], vocab), dtype=torch.float32, device=h.device))
+            z = cap * torch.tanh((z + self.w["bias"]) / cap)
+            if out is None:
+                return z
+            out.copy_(z)
+            return out
+
+    def recipe(cfg):
+        r = llama_recipe(cfg)
+        return dataclasses.replace(r, architecture="ToyEndsForCausalLM",
+                                   embedding=PartSpec("toy_scaled", {"name": "model.embed_tokens"}),
+                                   head=PartSpec("toy_soft_capped", {"name": "lm_head"}))
+
+    if "ToyEndsForCausalLM" not in registered_architectures():
+        register_architecture(Architecture("ToyEndsForCausalLM", "toy-ends-test", LlamaConfig.from_hf, recipe))
+    cfg = LlamaConfig(vocab_size=vocab, hidden_size=hidden, intermediate_size=80, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=96)
+    hf = cfg.to_hf()
+    hf["architectures"] = ["ToyEndsForCausalLM"]
+    write_random_model(tmp_path, hf, seed=15)
+    pcfg, w = plain.read_folder(tmp_path)
+    assert w["model.embed_tokens.offset"].dtype == torch.float32 and "lm_head.bias" in w
+
+    def plain_logits(ids):
+        positions = torch.arange(len(ids))
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)].float() * math.sqrt(hidden) + w["model.embed_tokens.offset"]
+        inv_freq = plain.plain_inv_freq(16, 10000.0, None)
+        for layer in range(2):
+            x = plain.plain_layer(x, w, layer, pcfg, positions, inv_freq)
+        z = plain.plain_rmsnorm(x, w["model.norm.weight"], pcfg["eps"]) @ w["lm_head.weight"].float().T + w["lm_head.bias"]
+        return cap * torch.tanh(z / cap)
+
+    model = load_model(tmp_path, device="cuda", dtype=torch.float32)
+    seqs = {0: random_ids(33, vocab, seed=31), 1: random_ids(12, vocab, seed=32)}
+    runner = ModelRunner(model, num_blocks=24, block_size=4, max_requests=2)
+    got = {r: [] for r in seqs}
+    runner.begin(0), runner.begin(1)
+    for entries in ([(0, 0, 10), (1, 0, 3)], [(1, 3, 4), (0, 10, 12)], [(0, 12, 33), (1, 4, 12)]):
+        out = runner.step([StepEntry(r, seqs[r][a:b], list(range(b - a))) for r, a, b in entries])
+        row = 0
+        for r, a, b in entries:
+            got[r].append(out[row: row + b - a].float().cpu())
+            row += b - a
+    runner.end(0), runner.end(1)
+    for r, ids in seqs.items():
+        torch.testing.assert_close(torch.cat(got[r]), plain_logits(ids), rtol=3e-5, atol=3e-6)
+    del runner
+
+    prompts = [seqs[0][:7], seqs[1][:3]]
+    for graphs in (True, False):
+        eng = Engine(model, EngineConfig(num_blocks=64, block_size=4, cuda_graphs=graphs, max_running=2))
+        outs = eng.generate(prompts, SamplingParams(max_tokens=6))
+        assert not graphs or eng.graphs.replays >= 4
+        for p, o in zip(prompts, outs):
+            ids = list(p)
+            for t in o:
+                z = plain_logits(ids)[-1]
+                top = z.topk(2).values
+                assert t == int(z.argmax()) or float(top[0] - top[1]) < 1e-5
+                ids.append(t)
