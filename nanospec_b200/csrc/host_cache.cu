@@ -426,6 +426,9 @@ NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens,
         kv_len[b] = (int)reqs[b]->seq_len;
         slots[b] = reqs[b]->slot;
     }
+    // the decode attention kernel's blocks are scheduled in this order: the requests with the most keys first, so that
+    // no long one starts when the others are done
+    std::stable_sort(decode_rows, decode_rows + d, [&](int x, int y) { return kv_len[token_req[x]] > kv_len[token_req[y]]; });
     if (n_want) memcpy(buf + offsets[6], want_rows, sizeof(int) * n_want);
     if (n_take) {
         memcpy(buf + offsets[7], take_dst, sizeof(int) * n_take);

@@ -226,6 +226,18 @@ def test_a_steps_description_is_packed_natively_and_reserves_all_or_nothing():
     with pytest.raises(KeyError):
         pack([77], [1], [1])
     m.check()
+    # the rows that decode are listed with the longest contexts first (the order in which the kernel's blocks are scheduled)
+    big = CacheManager([(CacheNeed(2, 8, 0), None)], num_blocks=40, block_size=4, num_state_slots=5)
+    for r, n in ((1, 5), (2, 40), (3, 12), (4, 40)):
+        big.begin(r)
+        big.extend(r, n)
+    big.begin(8)
+    a = lambda x, t=np.int32: np.asarray(list(x), dtype=t)
+    offsets, _, counts, _, _, _ = big.pack_step(a([1, 2, 8, 3, 4], np.int64), a([1, 1, 3, 1, 1]), a(range(7)), a(()), a(()), a(()), a(()),
+                                                (2, 4), 64, buf, 256)
+    assert counts[0] == 4 and counts[3] == 41
+    assert buf[offsets[9]: offsets[9] + 4].tolist() == [1, 6, 5, 0]  # requests 2 and 4 (41 keys, in their order), 3 (13), 1 (6)
+    big.check()
 
 
 def test_a_decode_steps_description_for_a_graph_bucket():

@@ -172,6 +172,31 @@ def test_more_than_64_requests_decode_from_the_graph_of_128(dtype, wide_folders)
     assert eng.cache.live == []
 
 
+def test_decode_rows_run_longest_context_first(tiny_folders):
+    """A decode step's rows are ordered by context length, longest first (the order in which the decode attention
+    kernel's blocks are scheduled), in graph replays and in eager steps alike; the tokens do not depend on it."""
+    folder = tiny_folders["B"]
+    spec = TINY["B"]
+    cfg, w = plain.read_folder(folder)
+    model = load(folder, torch.float32)
+    vocab = spec["config"].vocab_size
+    prompts = [random_ids(n, vocab, seed=40 + n) for n in (3, 30, 11, 30, 7)]
+    for graphs in (True, False):
+        eng = engine(model, num_blocks=64, block_size=spec["page"], cuda_graphs=graphs, max_admit=8)
+        reqs = [eng.add(p, params(max_tokens=6)) for p in prompts]
+        seen = 0
+        while eng.sched.has_work:
+            eng.step()
+            flight = eng._inflight
+            if flight is not None and all(len(s.tokens) == 1 for s in flight.batch):
+                lengths = [s.req.committed for s in flight.batch]
+                assert lengths == sorted(lengths, reverse=True), lengths
+                seen += 1
+        assert seen >= 3
+        for req, p in zip(reqs, prompts):
+            assert req.out_tokens == plain.plain_greedy(cfg, w, p, 6)[0]
+
+
 def test_a_frozen_workspace_refuses_to_grow():
     from nanospec_b200.parts.context import Workspace
 
