@@ -48,7 +48,7 @@ _SIGNATURES = {
     "ns_cache_take_fresh": [_P, _PI, _I],
     "ns_cache_check": [_P],
     "ns_step_pack": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _PI, _L, _P, _L, _PI, _PI, _PL, _PL, _PI, _PL],
-    "ns_step_pack_decode": [_P, _I, _I, _P, _L, _I, _P, _I, _I, _I, _I, _PI, _I],
+    "ns_step_pack_decode": [_P, _I, _I, _P, _L, _I, _P, _I, _I, _I, _I, _PI, _I, _I, _I],
 }
 _declared = False
 
@@ -284,10 +284,11 @@ class CacheManager:
         numpy array of `cap` entries): see ns_step_pack in csrc/host_cache.cu for the layout.  The arguments are
         contiguous numpy arrays (int64 ids, int32 the rest; `extra` is copied along as it is).  Returns (offsets,
         table widths, counts, total, longest portion, longest sequence) with counts = (one-token requests, query
-        tiles of tile_q[0], of tile_q[1], longest sequence among the one-token requests); raises BufferError with
-        the ints needed when `buf` is too small (nothing changed)."""
+        tiles of tile_q[0], of tile_q[1], longest sequence among the one-token requests, items of the decode work
+        list, slots of scratch it needs); raises BufferError with the ints needed when `buf` is too small (nothing
+        changed)."""
         G = self._n_groups
-        offsets, widths, counts = (c_int * (13 + G))(), (c_int * max(G, 1))(), (c_longlong * 4)()
+        offsets, widths, counts = (c_int * (14 + G))(), (c_int * max(G, 1))(), (c_longlong * 6)()
         total, max_q, max_kv = c_longlong(), c_int(), c_longlong()
         status = self._lib.ns_step_pack(
             self._h, len(req_ids), req_ids.ctypes.data, q_lens.ctypes.data, tokens.ctypes.data, len(want_rows),
@@ -299,11 +300,14 @@ class CacheManager:
         self._status(status)
         return list(offsets), list(widths[:G]), list(counts), total.value, max_q.value, max_kv.value
 
-    def pack_decode(self, req_ids, size: int, max_positions: int, buf, off: dict[str, int], table_off, width: int) -> None:
-        """The description of a decode-only step padded to a graph bucket of `size` rows (ns_step_pack_decode)."""
+    def pack_decode(self, req_ids, size: int, max_positions: int, buf, off: dict[str, int], table_off, width: int,
+                    n_work: int = 0) -> None:
+        """The description of a decode-only step padded to a graph bucket of `size` rows (ns_step_pack_decode); with
+        `n_work` also the decode attention kernel's work list of that many items at off["work"]."""
         self._status(self._lib.ns_step_pack_decode(
             self._h, len(req_ids), size, req_ids.ctypes.data, max_positions, self.scratch_slot, buf.ctypes.data,
-            off["positions"], off["token_req"], off["kv_len"], off["slots"], table_off, width))
+            off["positions"], off["token_req"], off["kv_len"], off["slots"], table_off, width,
+            off.get("work", 0) if n_work else 0, n_work))
 
     # ---- invariants ---------------------------------------------------------------------
     def check(self) -> None:

@@ -17,6 +17,13 @@
 // cluster barrier it adds them in split order - no scratch in global memory, no atomics, and a
 // result that does not depend on timing.  Launch dimensions do not depend on sequence lengths.
 //
+// A batch whose contexts differ much in length would leave the blocks of the longest request streaming alone long
+// after the others are done.  The host therefore may hand the kernel a work list instead of rows: items (token row,
+// request, keys the request sees, group) in which a long request appears several times, each time for a part of its
+// keys.  A cluster then stores its result unnormalised (with the maxima and sums) in global memory, counts itself
+// in, and the block that finds the request's other parts complete adds them up in the order of the parts.  An item
+// holds all that the kernel otherwise reads from the step's description, one load instead of a chain of three.
+//
 // Tokens whose request brings more than one token are left to the prefill kernel; padding rows
 // (request index < 0) are skipped.  Page sizes 8, 16, 32, 64.  Every mbarrier wait is bounded; a
 // wait that runs out sets *error_flag and the block winds down through the same barriers.
@@ -51,6 +58,43 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t tile, int row, int col) {
            (uint32_t)((((col & 63) >> 3) ^ (row & 7)) << 4);
 }
 
+// one part of a request that the work list has cut up, per (kv head, head tile): [16 rows][D] sums, then [16][maximum, sum]
+template <int D>
+constexpr int kPartFloats = 16 * D + 32;
+
+// Every block that has stored its share of a part counts itself in; the one that completes the count (parts x splits
+// blocks) finds all the parts in global memory and adds them up in the order of the parts.  The counter goes back to
+// zero for the next launch.
+template <int D>
+__device__ __forceinline__ void merge_parts(const float* part, int* counters, int meta, int n_splits, __nv_bfloat16* out_row,
+                                            int total) {
+    __shared__ int last;
+    const int first = meta >> 8, parts = meta & 15;
+    __threadfence();       // this thread's stores are visible before the count below
+    __syncthreads();
+    int* counter = counters + (size_t)first * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) last = atomicAdd(counter, 1) == parts * n_splits - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();       // the other blocks' stores, counted before this block's, are visible to the loads below
+    const float* p0 = part + ((size_t)first * gridDim.y + blockIdx.y) * kPartFloats<D>;
+    const size_t stride = (size_t)gridDim.y * kPartFloats<D>;
+    for (int e = threadIdx.x; e < total; e += kDtThreads) {
+        const int row = e / D;
+        float mt = -INFINITY;
+        for (int c = 0; c < parts; ++c) mt = fmaxf(mt, __ldcg(p0 + c * stride + 16 * D + 2 * row));
+        float acc = 0.f, lt = 0.f;
+        for (int c = 0; c < parts; ++c) {
+            const float ms = __ldcg(p0 + c * stride + 16 * D + 2 * row);
+            const float f = ms == -INFINITY ? 0.f : ns_exp2(ms - mt);
+            acc += __ldcg(p0 + c * stride + e) * f;
+            lt += __ldcg(p0 + c * stride + 16 * D + 2 * row + 1) * f;
+        }
+        out_row[e] = __float2bfloat16_rn(acc / lt);
+    }
+    if (threadIdx.x == 0) *counter = 0;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kDtThreads, 2)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -58,7 +102,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             int table_stride, const int* __restrict__ token_req, const int* __restrict__ positions,
                             const int* __restrict__ qo_indptr, __nv_bfloat16* __restrict__ out, int o_stride,
                             const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
-                            int head_tiles, int* __restrict__ error_flag) {
+                            int head_tiles, int* __restrict__ error_flag, const int4* __restrict__ work,
+                            float* __restrict__ part, int* __restrict__ counters) {
     ns_pdl_launch_dependents();
     constexpr int kDtStages = dt_stages<D>();
     constexpr int kTileBytes = kKeys * D * 2;      // the keys or the values of one tile
@@ -93,21 +138,37 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // the tile that holds the token's own key (written earlier in this step) come after the wait.
 
     const int n_splits = gridDim.x, split = blockIdx.x, z = blockIdx.z;
-    const int n = rows ? rows[z] : z;  // the token this cluster works for
+    // the token this cluster works for; with a work list also its request, the keys it sees and the part of them that
+    // this item takes: meta = first slot << 8 | part << 4 | parts, or -1 for a whole request
+    int n, req, pos, meta = -1;
+    if (work) {
+        const int4 item = work[z];
+        n = item.x, req = item.y, pos = item.z - 1, meta = item.w;  // an unused item has request -1
+    } else {
+        n = rows ? rows[z] : z;
+        req = token_req[n];
+        if (req >= 0 && qo_indptr[req + 1] - qo_indptr[req] != 1) req = -1;  // not a decode row: the prefill kernel's
+        pos = req >= 0 ? positions[n] : 0;
+    }
     const int hk = blockIdx.y / head_tiles, ht = blockIdx.y - hk * head_tiles;
-    const int req = token_req[n];
     // (the same for every block of the cluster; a block with nothing to do still waits for the predecessor, so that
     // a grid of nothing but such blocks cannot complete before it and let its own successor start too early)
-    if (req < 0 || qo_indptr[req + 1] - qo_indptr[req] != 1) { ns_pdl_wait(); return; }
+    if (req < 0) { ns_pdl_wait(); return; }
     // a block's shared memory may be written by the others only once it runs: every block says so here
     // and checks the others before its first store into them
     if (n_splits > 1) cluster_arrive();
     const int G = nq / nkv;
     const int h0 = hk * G + ht * 16;
     const int gcount = min(16, G - ht * 16);
-    const int pos = positions[n];
-    const int kend = pos + 1;
-    const int kstart = (window > 0 && kend - window > 0) ? kend - window : 0;
+    int kend = pos + 1;
+    int kstart = (window > 0 && kend - window > 0) ? kend - window : 0;
+    if (meta >= 0) {
+        // part c of `parts`: whole tiles of 64 keys, as the packer counted them
+        const int parts = meta & 15, c = (meta >> 4) & 15;
+        const int each = (((kend + parts - 1) / parts + kKeys - 1) / kKeys) * kKeys;
+        kstart = c * each;
+        kend = min(kend, kstart + each);
+    }
     const int origin = kstart & ~(kKeys - 1);                  // tiles start on a page edge
     const int chunk = (((kend - origin + n_splits - 1) / n_splits + kKeys - 1) / kKeys) * kKeys;
     const int k0 = origin + split * chunk;
@@ -297,7 +358,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
         }
         if (n_splits == 1) {
-            out[(size_t)n * o_stride + (size_t)(h0 + row) * D + col] = __float2bfloat16_rn(acc / lt);
+            if (meta < 0) {
+                out[(size_t)n * o_stride + (size_t)(h0 + row) * D + col] = __float2bfloat16_rn(acc / lt);
+            } else {
+                float* slot = part + ((size_t)((meta >> 8) + ((meta >> 4) & 15)) * gridDim.y + blockIdx.y) * kPartFloats<D>;
+                slot[e] = acc;
+                if (col == 0) { slot[16 * D + 2 * row] = mt; slot[16 * D + 2 * row + 1] = lt; }
+            }
         } else {
             const int owner = e / per;
             st_cluster_f32(recv_o_addr + 4u * (uint32_t)(split * per + (e - owner * per)), (uint32_t)owner, acc);
@@ -309,7 +376,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
         }
     }
-    if (n_splits == 1) return;
+    if (n_splits == 1) {
+        if (meta >= 0) merge_parts<D>(part, counters, meta, n_splits, out + (size_t)n * o_stride + (size_t)h0 * D, total);
+        return;
+    }
 
     // ---- one cluster barrier, then every block merges its slice from its own shared memory, in split order ----
     cluster_sync();
@@ -330,16 +400,23 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 lt += recv_ml[(s2 * 16 + row) * 2 + 1] * f;
             }
         }
-        out[(size_t)n * o_stride + (size_t)h0 * D + e] = __float2bfloat16_rn(acc / lt);
+        if (meta < 0) {
+            out[(size_t)n * o_stride + (size_t)h0 * D + e] = __float2bfloat16_rn(acc / lt);
+        } else {
+            float* slot = part + ((size_t)((meta >> 8) + ((meta >> 4) & 15)) * gridDim.y + blockIdx.y) * kPartFloats<D>;
+            slot[e] = acc;
+            if (e - row * D == 0) { slot[16 * D + 2 * row] = mt; slot[16 * D + 2 * row + 1] = lt; }
+        }
     }
     // nothing reads another block's shared memory after the barrier: a block may exit when it is done
+    if (meta >= 0) merge_parts<D>(part, counters, meta, n_splits, out + (size_t)n * o_stride + (size_t)h0 * D, total);
 }
 
 template <int D>
 int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const int* block_table,
                       int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                       int o_stride, const int* rows, int n_tokens, int nq, int nkv, int page_size, float scale, int window,
-                      int n_splits, int* error_flag, cudaStream_t stream) {
+                      int n_splits, int* error_flag, const int* work, float* part, int* counters, cudaStream_t stream) {
     constexpr int kDtStages = dt_stages<D>();
     constexpr int kSmem = kDtStages * 2 * kKeys * D * 2 + (16 * D + kMaxClusterSplits + kMaxClusterSplits * 32) * 4 + 2 * kDtStages * 8 + 1024;
     static_assert(kDtStages * 2 * kKeys * D * 2 >= (kComputeWarps * 16 * (D + 8) + 128) * 4, "the warps' partial results reuse the stages");
@@ -373,7 +450,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
     cfg.numAttrs = n_attr;
     (void)cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<D>, mk, mv, (const __nv_bfloat16*)q, q_stride, block_table,
                              table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, rows, nq, nkv,
-                             page_size, scale, window, head_tiles, error_flag);
+                             page_size, scale, window, head_tiles, error_flag, (const int4*)work, part, counters);
     NS_CHECK_LAUNCH("ns_attention_decode_tma");
     return NS_OK;
 }
@@ -383,12 +460,19 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
 // bfloat16, head_dim 64 or 128, page sizes 8 to 64; k_cache, v_cache: one lane's pages
 // [n_pages, nkv, page_size, head_dim]; n_splits 1, 2, 4, 8 or 16 (the blocks of one cluster).
 // `rows` (optional) lists the token rows to work on (n_tokens of them).
+// `work` (optional, instead of rows; not with a window): n_tokens items of four ints (token row or -1 for an unused
+// item, first key, end key, meta) as the cache manager's packer writes them: a request whose context is much longer
+// than the others' appears once per part of its keys, meta = first slot << 8 | part << 4 | parts (at most 15 parts),
+// and -1 for a whole request.  `part` then holds (slots) x (kv heads x head tiles) x (16 x head_dim + 32) floats and
+// `counters` (slots) x (kv heads x head tiles) ints that are zero before the first launch (the kernel leaves them zero).
 NS_API int ns_attention_decode_tma(const void* q, int q_stride, const void* k_cache, const void* v_cache, long long n_pages,
                                    const int* block_table, int table_stride, const int* token_req, const int* positions,
                                    const int* qo_indptr, void* out, int o_stride, const int* rows, int n_tokens, int nq,
                                    int nkv, int d, int page_size, float scale, int window, int n_splits, int* error_flag,
-                                   cudaStream_t stream) {
+                                   const int* work, float* part, int* counters, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
+    if (work && (window > 0 || rows || !part || !counters || (uintptr_t)work % 16))
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode_tma: a work list goes without rows and without a window, with its scratch, 16-byte aligned");
     if (d != 64 && d != 128) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_tma: head_dim=%d (64 or 128)", d);
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode_tma: page_size=%d (8, 16, 32 or 64)", page_size);
@@ -407,7 +491,9 @@ NS_API int ns_attention_decode_tma(const void* q, int q_stride, const void* k_ca
     if (rc) return rc;
     if (d == 64)
         return launch_decode_tma<64>(mk, mv, q, q_stride, block_table, table_stride, token_req, positions, qo_indptr, out,
-                                     o_stride, rows, n_tokens, nq, nkv, page_size, scale, window, n_splits, error_flag, stream);
+                                     o_stride, rows, n_tokens, nq, nkv, page_size, scale, window, n_splits, error_flag, work, part,
+                                     counters, stream);
     return launch_decode_tma<128>(mk, mv, q, q_stride, block_table, table_stride, token_req, positions, qo_indptr, out,
-                                  o_stride, rows, n_tokens, nq, nkv, page_size, scale, window, n_splits, error_flag, stream);
+                                  o_stride, rows, n_tokens, nq, nkv, page_size, scale, window, n_splits, error_flag, work, part,
+                                  counters, stream);
 }

@@ -339,6 +339,60 @@ NS_API int ns_cache_check(void* h) {
 }
 
 // ---------------------------------------------------------------------------------------------------
+// The decode attention kernel's work list.  Its blocks are per request, so a request whose context is much longer
+// than the others' would stream alone long after they are done.  A request of at least twice the mean context is cut
+// into parts of about the mean (at least 512 keys, whole tiles of 64, at most 15 parts, and no more extra items than
+// `extra_cap`: the parts grow until they fit); each part is an item of its own, and the kernel adds the parts up.  Items are
+// (token row, request, keys the request sees, meta): meta = -1 for a whole request, else first slot << 8 | part << 4 |
+// parts, where part c of a request of `len` keys is the keys [c * each, min(len, (c + 1) * each)) with each =
+// ceil(len / parts) rounded up to whole tiles, and the request's parts take the slots first .. first + parts - 1
+// of the kernel's scratch.  The longest items come first: blocks are scheduled in that order.  `rows[i]` is the
+// token row of entry i, `reqs[i]` its row of the block tables, `lens[i]` the keys it sees.
+// ---------------------------------------------------------------------------------------------------
+struct WorkItem { int row, req, len, meta; };
+
+static std::vector<WorkItem> plan_decode_work(const std::vector<int>& rows, const std::vector<int>& req_rows,
+                                              const std::vector<long long>& lens, long long extra_cap, int* n_slots) {
+    const int n = (int)rows.size();
+    std::vector<WorkItem> items;
+    *n_slots = 0;
+    if (n == 0) return items;
+    long long total = 0;
+    for (long long v : lens) total += v;
+    long long part = std::max(512ll, ((total / n + 63) / 64) * 64);
+    // a request is cut only when it is at least twice as long as a part
+    auto parts_of = [&](long long len) { return (int)std::min(15ll, std::max(1ll, len / part)); };
+    for (;;) {
+        long long extra = 0;
+        for (long long v : lens) extra += parts_of(v) - 1;
+        if (extra <= extra_cap) break;
+        part *= 2;
+    }
+    struct Keyed { WorkItem item; long long keys; };
+    std::vector<Keyed> keyed;
+    keyed.reserve(n + (size_t)extra_cap);
+    for (int i = 0; i < n; ++i) {
+        int parts = std::max(1, parts_of(lens[i]));
+        // whole tiles: rounding a part up may leave the last parts empty; fewer parts then
+        while (parts > 1 && (long long)(parts - 1) * ((((lens[i] + parts - 1) / parts + 63) / 64) * 64) >= lens[i]) --parts;
+        if (parts == 1) {
+            keyed.push_back({{rows[i], req_rows[i], (int)lens[i], -1}, lens[i]});
+            continue;
+        }
+        const long long each = (((lens[i] + parts - 1) / parts + 63) / 64) * 64;
+        for (int c = 0; c < parts; ++c) {
+            const long long from = c * each, to = std::min(lens[i], from + each);
+            keyed.push_back({{rows[i], req_rows[i], (int)lens[i], (*n_slots << 8) | (c << 4) | parts}, to - from});
+        }
+        *n_slots += parts;
+    }
+    std::stable_sort(keyed.begin(), keyed.end(), [](const Keyed& x, const Keyed& y) { return x.keys > y.keys; });
+    items.reserve(keyed.size());
+    for (const Keyed& k : keyed) items.push_back(k.item);
+    return items;
+}
+
+// ---------------------------------------------------------------------------------------------------
 // One step's description.  Reserves pages for every entry (all of them, or none: NS_ERR_EXHAUSTED and
 // NS_ERR_ARGUMENT leave the cache as it was) and lays out, in `buf` (int32, 16-byte aligned sections):
 //   0 token ids [N]   1 positions [N]   2 request of each token [N]   3 qo_indptr [B+1]   4 kv_len [B]
@@ -347,8 +401,9 @@ NS_API int ns_cache_check(void* h) {
 //   10, 11 the query tiles of the requests that bring more, as (request, offset among its tokens) pairs, for tiles
 //      of tile_q[0] and of tile_q[1] queries [2 * counts[1]], [2 * counts[2]]; the tiles that see the most keys first
 //   12 whatever the caller wants copied along [n_extra] (the sampling options of the step's sampled rows)
-//   13.. one block table per group, [B, width] with width = the longest table among the entries (>= 1)
-// offsets[13 + groups], widths[groups]; counts[3] = the longest sequence among the one-token requests (0: none);
+//   13 the decode attention kernel's work list [4 * counts[4]] (see plan_decode_work; counts[5] slots of scratch)
+//   14.. one block table per group, [B, width] with width = the longest table among the entries (>= 1)
+// offsets[14 + groups], widths[groups]; counts[3] = the longest sequence among the one-token requests (0: none);
 // *total = ints used.  NS_ERR_SMALL (nothing changed) when cap is too small, with *total = what is needed.
 // ---------------------------------------------------------------------------------------------------
 NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens, const int* tokens, int n_want,
@@ -381,17 +436,34 @@ NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens,
         }
         for (int gi = 0; gi < G; ++gi) table_len[gi] = std::max(table_len[gi], c->groups[gi].blocks_for(end));
     }
+    // the work list of the requests that bring one token (their token rows are known already: rows run in entry order)
+    std::vector<int> work_rows, work_reqs;
+    std::vector<long long> work_lens;
+    {
+        long long row = 0;
+        for (int b = 0; b < B; ++b) {
+            if (q_lens[b] == 1) {
+                work_rows.push_back((int)row);
+                work_reqs.push_back(b);
+                work_lens.push_back(reqs[b]->seq_len + 1);
+            }
+            row += q_lens[b];
+        }
+    }
+    int n_slots = 0;
+    const std::vector<WorkItem> work = plan_decode_work(work_rows, work_reqs, work_lens, n_decode, &n_slots);
     long long at = 0;
-    const long long sizes[13] = {N, N, N, (long long)B + 1, B, B, n_want, n_take, n_take, n_decode, 2 * n_tiles[0], 2 * n_tiles[1],
-                                 n_extra};
-    for (int s = 0; s < 13; ++s) { offsets[s] = (int)at; at += pad4(sizes[s]); }
+    const long long sizes[14] = {N, N, N, (long long)B + 1, B, B, n_want, n_take, n_take, n_decode, 2 * n_tiles[0], 2 * n_tiles[1],
+                                 n_extra, 4 * (long long)work.size()};
+    for (int s = 0; s < 14; ++s) { offsets[s] = (int)at; at += pad4(sizes[s]); }
     for (int gi = 0; gi < G; ++gi) {
         widths[gi] = (int)table_len[gi];
-        offsets[13 + gi] = (int)at;
+        offsets[14 + gi] = (int)at;
         at += pad4((long long)B * table_len[gi]);
     }
     *total = at;
     counts[0] = n_decode, counts[1] = n_tiles[0], counts[2] = n_tiles[1], counts[3] = max_kv_decode;
+    counts[4] = (long long)work.size(), counts[5] = n_slots;
     if (at > cap) NS_FAIL(NS_ERR_SMALL, "ns_step_pack: the description needs %lld ints, the buffer holds %lld", at, cap);
     // reserve: everything or nothing
     std::vector<long long> before(B);
@@ -435,6 +507,7 @@ NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens,
         memcpy(buf + offsets[8], take_src, sizeof(int) * n_take);
     }
     if (n_extra) memcpy(buf + offsets[12], extra, sizeof(int) * n_extra);
+    if (!work.empty()) memcpy(buf + offsets[13], work.data(), sizeof(WorkItem) * work.size());
     // query tiles of the prompt portions; blocks are scheduled in this order, so the tiles that see the most keys
     // (the last ones of the longest sequences) come first
     struct Tile { int req, off; long long keys; };
@@ -451,7 +524,7 @@ NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens,
         for (size_t i = 0; i < tiles.size(); ++i) { out[2 * i] = tiles[i].req; out[2 * i + 1] = tiles[i].off; }
     }
     for (int gi = 0; gi < G; ++gi) {
-        int* table = buf + offsets[13 + gi];
+        int* table = buf + offsets[14 + gi];
         const int W = widths[gi];
         for (int b = 0; b < B; ++b) {
             const std::vector<int>& pages = reqs[b]->tables[gi].pages;
@@ -465,10 +538,11 @@ NS_API int ns_step_pack(void* h, int B, const long long* ids, const int* q_lens,
 // The description of a decode-only step of a captured graph's bucket: `size` rows of which the first B are
 // requests with one token each, the rest padding (request -1, length 0, the scratch state slot).  Reserves
 // one position per request (all or none) and writes positions, token_req, kv_len, slots and, for every group,
-// the block table rows of width `width` into `buf` at the given offsets.
+// the block table rows of width `width` into `buf` at the given offsets; with n_work > 0 also the decode attention
+// kernel's work list of exactly n_work items (16-byte aligned at off_work; at most n_work - B extra parts).
 NS_API int ns_step_pack_decode(void* h, int B, int size, const long long* ids, long long max_positions, int scratch_slot,
                                int* buf, int off_positions, int off_token_req, int off_kv_len, int off_slots,
-                               const int* table_off, int width) {
+                               const int* table_off, int width, int off_work, int n_work) {
     Cache* c = as_cache(h);
     const int G = (int)c->groups.size();
     if (B > size) NS_FAIL(NS_ERR_ARGUMENT, "ns_step_pack_decode: %d requests in a bucket of %d", B, size);
@@ -500,6 +574,17 @@ NS_API int ns_step_pack_decode(void* h, int B, int size, const long long* ids, l
         buf[off_token_req + b] = real ? b : -1;
         buf[off_kv_len + b] = real ? (int)reqs[b]->seq_len : 0;
         buf[off_slots + b] = real ? reqs[b]->slot : scratch_slot;
+    }
+    if (n_work > 0) {
+        // the work list of the bucket: n_work items, the unused ones with row -1
+        if (n_work < B) NS_FAIL(NS_ERR_ARGUMENT, "ns_step_pack_decode: a work list of %d items for %d requests", n_work, B);
+        std::vector<int> rows(B);
+        std::vector<long long> lens(B);
+        for (int b = 0; b < B; ++b) { rows[b] = b; lens[b] = reqs[b]->seq_len; }
+        int n_slots = 0;
+        const std::vector<WorkItem> work = plan_decode_work(rows, rows, lens, n_work - B, &n_slots);
+        WorkItem* out = reinterpret_cast<WorkItem*>(buf + off_work);
+        for (int i = 0; i < n_work; ++i) out[i] = i < (int)work.size() ? work[i] : WorkItem{-1, -1, 0, -1};
     }
     for (int gi = 0; gi < G; ++gi)
         for (int b = 0; b < B; ++b) {

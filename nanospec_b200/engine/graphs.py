@@ -15,6 +15,7 @@ device buffer per step; the graph's kernels hold pointers into that device buffe
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 
 import numpy as np
 import torch
@@ -40,12 +41,15 @@ class _Bucket:
         m = runner.manager
         n_groups = len(m.groups)
         names = ["positions", "token_req", "qo_indptr", "kv_len", "slots", "want_rows", "top_k",
-                 "temperature", "top_p", "u", "take_dst", "take_src"]
+                 "temperature", "top_p", "u", "take_dst", "take_src", "work"]
+        # the decode attention kernel's work list: a request whose context is much longer than the others' comes in parts,
+        # each an item of its own; the bucket has room for this many items beyond its rows
+        self.n_work = size + min(size, 16)
         self.off: dict[str, int] = {}
         total = 0
         for nm in names:
             self.off[nm] = total
-            total += _pad4(size + 1 if nm == "qo_indptr" else size)
+            total += _pad4(4 * self.n_work if nm == "work" else size + 1 if nm == "qo_indptr" else size)
         self.table_off = []
         for _ in range(n_groups):
             self.table_off.append(total)
@@ -75,6 +79,7 @@ class _Bucket:
         # fixed parts of the description
         self.host_np[self.off["qo_indptr"]: self.off["qo_indptr"] + size + 1] = np.arange(size + 1, dtype=np.int32)
         self.host_np[self.off["want_rows"]: self.off["want_rows"] + size] = np.arange(size, dtype=np.int32)
+        self.host_np[self.off["work"]: self.off["work"] + 4 * self.n_work] = np.tile(np.array([-1, -1, 0, -1], dtype=np.int32), self.n_work)
         self._fill_padding(0, description=True)
         self.dev.copy_(self.host)
 
@@ -92,10 +97,21 @@ class _Bucket:
             max_q_len=1, max_kv_len=table_width * runner.block_size,
         )
         self.ctx.extras["graph"] = True
+        # Two graphs per bucket.  The usual one runs the decode attention kernel over the first `size` items of the work list
+        # (the rows, longest context first).  When some request's context is so much longer than the others' that the
+        # packer has cut it into parts, the list is longer than the bucket, and a second graph, captured when that
+        # first happens, runs the kernel over all `n_work` items (the unused ones cost a little, which is why the
+        # usual graph does without them).
+        plan = {"decode_rows": None, "n_decode": size, "tiles": None, "tiles_tc": None, "max_kv_len": None,
+                "work": view("work", 4 * size), "work_slots": 2 * (self.n_work - size)}
+        self.ctx.extras["attention_plan"] = plan
+        self.ctx_parts = dataclasses.replace(self.ctx, extras=dict(self.ctx.extras, attention_plan=dict(plan, work=view("work", 4 * self.n_work))))
         self.want_rows = view("want_rows", size)
         self.sampling = (view("temperature", size, torch.float32), view("top_k", size), view("top_p", size, torch.float32),
                          view("u", size, torch.float32))
-        self._capture(runner, pool)
+        self.blank = self.dev.clone()  # the description of a step of nothing but padding rows: what a capture runs on
+        self.graph_parts: torch.cuda.CUDAGraph | None = None
+        self.graph = self._capture(runner, pool, self.ctx)
 
     def _fill_padding(self, first: int, description: bool = False) -> None:
         """Sampling options and token ids of the rows from `first` on; with `description` also their request (-1),
@@ -112,20 +128,31 @@ class _Bucket:
         self.host_f32[o["top_p"] + first: o["top_p"] + n] = 1.0
         self.host_f32[o["u"] + first: o["u"] + n] = 0.0
 
-    def _forward(self, runner: ModelRunner) -> None:
-        hidden = runner.model.forward(self.ctx, self.want_rows)
+    def graph_for(self, runner: ModelRunner, pool, parts: bool) -> torch.cuda.CUDAGraph:
+        """The graph to replay: the usual one, or the one whose attention kernel takes the whole work list (captured at its
+        first use, on a description of padding rows, before the step's own description is copied in)."""
+        if not parts:
+            return self.graph
+        if self.graph_parts is None:
+            self.dev.copy_(self.blank)
+            self.ids_dev.fill_(-1)
+            self.graph_parts = self._capture(runner, pool, self.ctx_parts)
+        return self.graph_parts
+
+    def _forward(self, runner: ModelRunner, ctx: StepContext) -> None:
+        hidden = runner.model.forward(ctx, self.want_rows)
         z = runner.model.logits(hidden, self.logits)
         t, k, p, u = self.sampling
         ops.sample_rows(z, t, k, p, u, out=(self.out_token, self.out_lp[0], self.out_lp[1]), scratch=self.sample_scratch)
 
-    def _capture(self, runner: ModelRunner, pool) -> None:
+    def _capture(self, runner: ModelRunner, pool, ctx: StepContext) -> torch.cuda.CUDAGraph:
         # two eager runs on a side stream first (every row is padding, nothing touches the cache),
         # so that scratch buffers and library workspaces exist before the capture
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._forward(runner)
+                self._forward(runner, ctx)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         from ..ops import lib
@@ -133,10 +160,10 @@ class _Bucket:
         g = torch.cuda.CUDAGraph()
         before = lib.launch_count()
         with torch.cuda.graph(g, pool=pool):
-            self._forward(runner)
+            self._forward(runner, ctx)
         self.kernels = lib.launch_count() - before  # this framework's kernels in one replay
-        self.graph = g
         self.workspace.frozen = True  # a buffer that would have to move now raises instead
+        return g
 
 
 class DecodeGraphs:
@@ -188,12 +215,15 @@ class DecodeGraphs:
         o, hn, hf = bk.off, bk.host_np, bk.host_f32
         # pages for one more position of every request (all or none), then positions, lengths, state slots, padding
         # rows and every group's block-table rows, written by the cache manager's native side
-        m.pack_decode(req_ids, bk.size, runner.max_positions, hn, o, bk.table_off_c, bk.width)
+        m.pack_decode(req_ids, bk.size, runner.max_positions, hn, o, bk.table_off_c, bk.width, bk.n_work)
         hn[o["top_k"]: o["top_k"] + B] = [s.req.params.top_k for s in batch]
         hf[o["temperature"]: o["temperature"] + B] = [s.req.params.temperature for s in batch]
         hf[o["top_p"]: o["top_p"] + B] = [s.req.params.top_p for s in batch]
         hf[o["u"]: o["u"] + B] = uniforms
         bk._fill_padding(B)
+        # has the packer cut some request's keys into parts?  (meta of an item: -1 for a whole request)
+        w0 = o["work"]
+        graph = bk.graph_for(runner, self.pool, bool((hn[w0 + 3: w0 + 4 * bk.n_work: 4] >= 0).any()))
         t0 = t1 = None
         if self.timing is not None:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -217,7 +247,7 @@ class DecodeGraphs:
                          bk.dev[o["take_src"]: o["take_src"] + n_take])
         runner.h2d_bytes_last = (bk.total + bk.size) * 4
         runner.storage.zero_state_slots(m.take_fresh_slots())
-        bk.graph.replay()
+        graph.replay()
         self.replays += 1
         turn = bk.turn
         bk.turn ^= 1

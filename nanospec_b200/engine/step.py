@@ -156,7 +156,7 @@ class ModelRunner:
 
         if len(take_dst):
             ops.take_ids(view(0, N), view(7, len(take_dst)), take[1], view(8, len(take_src)))
-        group_tables = [view(13 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
+        group_tables = [view(14 + gi, B * widths[gi]).view(B, widths[gi]) for gi in range(len(m.groups))]
         self.storage.zero_state_slots(m.take_fresh_slots())
         host_np = host.numpy()
         kv_lens = host_np[offsets[4]: offsets[4] + B].tolist()
@@ -172,13 +172,16 @@ class ModelRunner:
         ctx.extras["req_ids"] = req_ids
         ctx.extras["extra"] = view(12, len(extra_np))
         # which token rows decode and the query tiles of the prompt portions (ops.attention reads this)
-        n_decode, n_a, n_b, max_kv_decode = counts
+        n_decode, n_a, n_b, max_kv_decode, n_work, work_slots = counts
         ctx.extras["attention_plan"] = {
             "n_decode": n_decode,
             "decode_rows": None if n_decode == N or not n_decode else view(9, n_decode),
             "tiles": view(10, 2 * n_a).view(n_a, 2) if n_a else None,
             "tiles_tc": view(11, 2 * n_b).view(n_b, 2) if n_b else None,
             "max_kv_len": max_kv_decode or None,
+            # the decode kernel's work list (a request much longer than the others comes in parts) and the slots of
+            # scratch that its parts need
+            "work": view(13, 4 * n_work) if n_work else None, "work_slots": work_slots,
         }
         n_want = len(want_rows)
         return ctx, (view(6, n_want) if n_want else None), n_want

@@ -523,20 +523,34 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 
 
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-                     window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None) -> None:
+                     window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
+                     work: torch.Tensor | None = None, work_slots: int = 0) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
     memory (csrc/attention_decode.cu).
-    `rows`: int32 device tensor of their token rows, or None when every row of the step is one."""
+    `rows`: int32 device tensor of their token rows, or None when every row of the step is one.
+    `work` (int32, four per item, from the cache manager's packer) replaces `rows` for the TMA kernel on lanes without
+    a window: a request whose context is much longer than the others' comes as several items, a part of its keys
+    each, and the kernel adds the parts up through `work_slots` slots of scratch."""
     head_tiles = -(-(nq // nkv) // 16)
     if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
+        if work is not None and window == 0:
+            ws = ctx.workspace
+            part = ws.get("attn_work_parts", max(work_slots, 1) * nkv * head_tiles, 16 * head_dim + 32, torch.float32)
+            counters = ws.get("attn_work_counters", max(work_slots, 1) * nkv * head_tiles, 1, torch.int32, zero=True)
+            lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+                     lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
+                     ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), None,
+                     work.numel() // 4, nq, nkv, head_dim, lane.page_size, float(scale), 0, n_splits,
+                     _tc(qkv.device).error.data_ptr(), work.data_ptr(), part.data_ptr(), counters.data_ptr(), _stream())
+            return
         lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
                  lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
                  ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), _ptr(rows), n_rows, nq,
                  nkv, head_dim, lane.page_size, float(scale), int(window), n_splits, _tc(qkv.device).error.data_ptr(),
-                 _stream())
+                 None, None, None, _stream())
         return
     n_splits = max(1, min(16, -(-_target_blocks() // (n_rows * nkv * head_tiles))))
     if max_kv_len is not None:
@@ -640,13 +654,13 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"])
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0))
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"])
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0))
     if plan["tiles"] is not None:
         attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
     return out

@@ -32,7 +32,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "ns_sample_rows": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "ns_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "ns_attention_decode_tma": [_P, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "ns_attention_decode_tma": [_P, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _P],
     "ns_gemm_bf16_tc_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _P, _P],
     "ns_rope_token_kernel_from": [_I],
     "ns_gemm_bf16_tc_rope": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I,

@@ -204,13 +204,14 @@ def test_a_steps_description_is_packed_natively_and_reserves_all_or_nothing():
     offsets, widths, counts, total, max_q, max_kv = pack([5, 9], [1, 3], [40, 41, 42, 43], want=[0, 3])
     assert (max_q, max_kv, widths) == (3, 7, [2, 2]) and all(o % 4 == 0 for o in offsets) and total <= 256
     # one request decodes (row 0, 7 positions); the other's 3 tokens make two query tiles of 2 and one of 4
-    assert counts == [1, 2, 1, 7]
+    assert counts == [1, 2, 1, 7, 1, 0]  # ... and one item in the decode work list, no request cut into parts
     sec = lambda i, n: buf[offsets[i]: offsets[i] + n].tolist()
     assert sec(0, 4) == [40, 41, 42, 43] and sec(1, 4) == [6, 0, 1, 2] and sec(2, 4) == [0, 1, 1, 1]
     assert sec(3, 3) == [0, 1, 4] and sec(4, 2) == [7, 3] and sec(5, 2) == [0, 1] and sec(6, 2) == [0, 3]
     assert sec(9, 1) == [0] and sec(10, 4) == [1, 2, 1, 0] and sec(11, 2) == [1, 0] and sec(12, 3) == [11, 12, 13]
+    assert sec(13, 4) == [0, 0, 7, -1]  # (token row, request, keys it sees, whole)
     for gi in (0, 1):
-        table = buf[offsets[13 + gi]: offsets[13 + gi] + 4].reshape(2, 2).tolist()
+        table = buf[offsets[14 + gi]: offsets[14 + gi] + 4].reshape(2, 2).tolist()
         assert table[0] == m.table(gi, 5) and table[1] == m.table(gi, 9) + [0]
     assert m.seq_len[5] == 7 and m.seq_len[9] == 3 and m.free_pages() == [3, 3]
     m.check()
@@ -237,7 +238,88 @@ def test_a_steps_description_is_packed_natively_and_reserves_all_or_nothing():
                                                 (2, 4), 64, buf, 256)
     assert counts[0] == 4 and counts[3] == 41
     assert buf[offsets[9]: offsets[9] + 4].tolist() == [1, 6, 5, 0]  # requests 2 and 4 (41 keys, in their order), 3 (13), 1 (6)
+    # contexts this short are never cut: the work list is the same rows, whole
+    assert counts[4:] == [4, 0] and buf[offsets[13]: offsets[13] + 16].reshape(4, 4).tolist() == [
+        [1, 1, 41, -1], [6, 4, 41, -1], [5, 3, 13, -1], [0, 0, 6, -1]]
     big.check()
+
+
+def test_a_long_request_among_short_ones_comes_in_parts():
+    """The decode work list: a context much longer than the mean is cut into parts of whole tiles of 64 keys, the
+    longest items first, every key of every request exactly once, the parts' slots distinct; a bucket's list is
+    padded with unused items and never has more extra items than it has room for."""
+    import numpy as np
+
+    lens = {1: 7900, 2: 200, 3: 150, 4: 5000, 5: 64, 6: 1}  # mean 2,219: parts of 2,240 keys; 7,900 makes three, 5,000 two
+    m = CacheManager([(CacheNeed(2, 8, 0), None)], num_blocks=900, block_size=16, num_state_slots=8)
+    for r, n in lens.items():
+        m.begin(r)
+        m.extend(r, n - 1)
+    a = lambda x, t=np.int32: np.asarray(list(x), dtype=t)
+    buf = np.zeros(8192, dtype=np.int32)
+
+    def covered(items):
+        """{row: None for a whole request, else its parts as (part, first key, end key, first slot, parts)}"""
+        seen = {}
+        slots = []
+        for row, req, n, meta in items:
+            if row < 0:
+                assert req == -1 and meta == -1
+                continue
+            assert req == row and n == list(lens.values())[row]
+            if meta < 0:
+                assert row not in seen
+                seen[row] = None
+            else:
+                first, c, parts = meta >> 8, (meta >> 4) & 15, meta & 15
+                each = -(-(-(-n // parts)) // 64) * 64
+                lo, hi = c * each, min(n, (c + 1) * each)
+                assert 2 <= parts <= 15 and c < parts and lo < hi
+                seen.setdefault(row, []).append((c, lo, hi, first, parts))
+                slots.append(first + c)
+        assert len(set(slots)) == len(slots) and sorted(slots) == list(range(len(slots)))
+        return seen
+
+    # an eager step: six decoding requests (rows 0..5)
+    offsets, _, counts, _, _, _ = m.pack_step(a(lens, np.int64), a([1] * 6), a(range(6)), a(()), a(()), a(()), a(()), (2, 4), 8192, buf, 8192)
+    n_items, n_slots = counts[4:]
+    items = buf[offsets[13]: offsets[13] + 4 * n_items].reshape(n_items, 4).tolist()
+    seen = covered(items)
+    assert sorted(seen) == list(range(6))
+    for row, n in enumerate(lens.values()):
+        if seen[row] is None:
+            assert n < 2 * 2240  # a whole request is shorter than two parts
+            continue
+        parts = sorted(seen[row])
+        assert [p[0] for p in parts] == list(range(len(parts))) and parts[0][1] == 0 and parts[-1][2] == n
+        assert all(x[2] == y[1] for x, y in zip(parts, parts[1:])) and len({(p[3], p[4]) for p in parts}) == 1
+    assert len(seen[0]) == 3 and len(seen[3]) == 2 and n_slots == 5
+    def keys_of(row, n, meta):
+        if meta < 0:
+            return n
+        c, parts = (meta >> 4) & 15, meta & 15
+        each = -(-(-(-n // parts)) // 64) * 64
+        return min(n, (c + 1) * each) - c * each
+
+    sizes = [keys_of(row, n, meta) for row, _, n, meta in items]
+    assert sizes == sorted(sizes, reverse=True)
+    for r in lens:
+        m.rollback(r, lens[r] - 1)
+    # a graph bucket of 8 rows with room for 3 extra items: the parts grow until they fit
+    off = {"positions": 0, "token_req": 8, "kv_len": 16, "slots": 24, "work": 32}
+    table_off = (__import__("ctypes").c_int * 1)(128)
+    m.pack_decode(a(lens, np.int64), 8, 8192, buf, off, table_off, 512, n_work=9)
+    items = buf[32: 32 + 36].reshape(9, 4).tolist()
+    seen = covered(items)
+    assert sorted(seen) == list(range(6)) and sum(1 for it in items if it[0] < 0) == 0
+    assert sum(len(v) - 1 for v in seen.values() if v) == 3
+    # room for two: parts twice as long, and neither request is twice as long as those
+    for r in lens:
+        m.rollback(r, lens[r] - 1)
+    m.pack_decode(a(lens, np.int64), 8, 8192, buf, off, table_off, 512, n_work=8)
+    items = buf[32: 32 + 32].reshape(8, 4).tolist()
+    assert all(v is None for v in covered(items).values()) and sum(1 for it in items if it[0] < 0) == 2
+    m.check()
 
 
 def test_a_decode_steps_description_for_a_graph_bucket():

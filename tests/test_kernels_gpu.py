@@ -383,7 +383,7 @@ def test_cluster_decode_attention(nq, nkv, d, page, window):
             lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
                      lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
                      ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), rows.data_ptr(),
-                     len(lens), nq, nkv, d, page, 1.0 / math.sqrt(d), window, n_splits, err.data_ptr(),
+                     len(lens), nq, nkv, d, page, 1.0 / math.sqrt(d), window, n_splits, err.data_ptr(), None, None, None,
                      torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             o.check_kernel_errors()
@@ -391,6 +391,41 @@ def test_cluster_decode_attention(nq, nkv, d, page, window):
                 full = plain.plain_attention(q, k, v, window=window)
                 torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
             assert float(out[len(lens):].abs().sum()) == 0.0  # the prompt portion's rows are not touched
+    if window:
+        return
+    # The same rows through a work list in which the long requests come in parts (two, five, and three of which the last
+    # holds two keys), an unused item sits in the middle, and the items are not in row order: the parts are added up
+    # by whichever block finishes last, and the counters are left at zero for the next launch.
+    items, slot = [], 0
+    cuts = {6: 2, 7: 5, 5: 3}
+    for r, S in enumerate(lens):
+        if r in cuts:
+            for c in range(cuts[r]):
+                items.append((r, r, S, (slot << 8) | (c << 4) | cuts[r]))
+            slot += cuts[r]
+        else:
+            items.append((r, r, S, -1))
+    items.insert(3, (-1, -1, 0, -1))
+    items = items[::-1]
+    work = torch.tensor(items, dtype=torch.int32, device=DEV).contiguous()
+    head_tiles = -(-(nq // nkv) // 16)
+    part = torch.full((slot * nkv * head_tiles, 16 * d + 32), float("nan"), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(slot * nkv * head_tiles, dtype=torch.int32, device=DEV)
+    for n_splits in (1, 2, 4, 16):
+        for _ in range(2):
+            out = torch.zeros(ctx.n_tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+            lib.call("ns_attention_decode_tma", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+                     lane.k.shape[0], lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(),
+                     ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), None,
+                     len(items), nq, nkv, d, page, 1.0 / math.sqrt(d), 0, n_splits, err.data_ptr(), work.data_ptr(),
+                     part.data_ptr(), counters.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            o.check_kernel_errors()
+            assert int(counters.abs().sum()) == 0
+            for r, (q, k, v, start) in enumerate(want[:-1]):
+                full = plain.plain_attention(q, k, v)
+                torch.testing.assert_close(out[r].float().cpu().view(nq, d), full[start], rtol=3e-2, atol=3e-2)
+            assert float(out[len(lens):].abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize("nq,nkv,page,d", [(8, 2, 16, 128), (4, 4, 8, 128), (6, 1, 32, 128), (32, 8, 64, 128), (8, 2, 16, 64), (6, 3, 8, 64),

@@ -197,6 +197,39 @@ def test_decode_rows_run_longest_context_first(tiny_folders):
             assert req.out_tokens == plain.plain_greedy(cfg, w, p, 6)[0]
 
 
+@pytest.mark.parametrize("name", ["wide128", "wide64"])
+def test_a_long_request_beside_short_ones_decodes_in_parts(name, tmp_path):
+    """One context of 2,100 tokens among contexts of a few dozen: the packer cuts the long one into four parts, each an
+    item of the decode attention kernel's work list, and the kernel adds the parts up.  Graph replays take the bucket's
+    second graph (captured when it is first needed, in the middle of the run); eager steps take the list as it is.
+    Every step's logits against the plain implementation; when the long request has ended the usual graph is back."""
+    import dataclasses
+
+    from nanospec_b200.weights import write_random_model
+
+    write_random_model(tmp_path, dataclasses.replace(WIDE[name], max_position_embeddings=2304), seed=77)
+    cfg, w = plain_on_gpu(tmp_path)
+    model = load(tmp_path, torch.bfloat16)
+    vocab = WIDE[name].vocab_size
+    prompts = [random_ids(n, vocab, seed=500 + n) for n in (21, 2100, 33, 48, 5)]
+    limits = [30, 12, 30, 30, 30]
+    for graphs in (True, False):
+        eng = engine(model, num_blocks=200, block_size=16, cuda_graphs=graphs, record_logits=True, max_admit=8)
+        reqs = [eng.add(p, params(max_tokens=n)) for p, n in zip(prompts, limits)]
+        while eng.sched.has_work:
+            eng.step()
+        if graphs:
+            assert eng.graphs.buckets[8].graph_parts is not None and eng.graphs.buckets[4].graph_parts is None
+            assert eng.graphs.replays >= 25
+        check_teacher_forced(reqs, prompts, cfg, w, torch.bfloat16, f"{name}, a long request in parts, graphs={graphs}")
+        eng.cache.check()
+    # launched ahead, without the recorded logits: the same tokens (but for a near-tie)
+    eng = engine(model, num_blocks=200, block_size=16, max_admit=8)
+    outs = eng.generate(prompts, [params(max_tokens=n) for n in limits])
+    assert sum(a == r.out_tokens for a, r in zip(outs, reqs)) >= 4
+    assert eng.launched_ahead >= 20
+
+
 def test_a_frozen_workspace_refuses_to_grow():
     from nanospec_b200.parts.context import Workspace
 
