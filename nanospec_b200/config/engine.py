@@ -27,7 +27,7 @@ class EngineConfig:
     prefill_chunk: int = 2048            # longest portion of one prompt in one step
     admission: str = "reserve"           # "reserve": worst-case page reservation, never preempts;
                                          # "optimistic": admit on current need, preempt the newest when pages run out
-    graph_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128)  # the reference stops at 64 (engine/graphs.py:22)
+    graph_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256)  # the reference stops at 64 (engine/graphs.py:22)
     lookahead: bool = True               # launch the next decode step before the last one's tokens reach the host
     capture_at_start: bool = True        # capture every bucket's graph when the engine is built, not at first use
 

@@ -167,7 +167,7 @@ class _Bucket:
 
 
 class DecodeGraphs:
-    def __init__(self, runner: ModelRunner, buckets=(1, 2, 4, 8, 16, 32, 64, 128), record_logits: bool = False) -> None:
+    def __init__(self, runner: ModelRunner, buckets=(1, 2, 4, 8, 16, 32, 64, 128, 256), record_logits: bool = False) -> None:
         self.runner = runner
         self.record_logits = record_logits
         self.sizes = tuple(sorted(buckets))

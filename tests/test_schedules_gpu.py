@@ -148,26 +148,28 @@ def test_graphs_captured_at_first_use_while_the_batch_grows(tmp_path):
     assert same >= len(reqs) - 4  # a near-tie may fall differently: the graphs' attention splits the keys otherwise
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_more_than_64_requests_decode_from_the_graph_of_128(dtype, wide_folders):
-    """The reference's graphs stop at 64 requests (engine/graphs.py:22); here 70 to 100 live requests replay the
-    bucket of 128 with its padding rows.  Every step's logits against the plain implementation."""
+@pytest.mark.parametrize("dtype,n_req", [("float32", 100), ("bfloat16", 100), ("bfloat16", 150)])
+def test_more_than_64_requests_decode_from_the_larger_graphs(dtype, n_req, wide_folders):
+    """The reference's graphs stop at 64 requests (engine/graphs.py:22); here 65 to 128 live requests replay the
+    bucket of 128 and 129 to 256 that of 256, with their padding rows.  Every step's logits against the plain
+    implementation."""
     dt = DTYPES[dtype]
     folder = wide_folders["wide64"]
     cfg, w = plain_on_gpu(folder)
     model = load(folder, dt)
     vocab = WIDE["wide64"].vocab_size
-    prompts = [random_ids(3 + (11 * i) % 40, vocab, seed=7000 + i) for i in range(100)]
-    plist = [params(max_tokens=3 + (i % 3) * 3) for i in range(100)]  # 100 live, then 67, then 34: buckets 128, 128, 64
-    eng = engine(model, num_blocks=500, block_size=16, record_logits=True, max_admit=128, max_running=128)
-    assert 128 in eng.graphs.buckets, "captured when the engine is built"
+    prompts = [random_ids(3 + (11 * i) % 40, vocab, seed=7000 + i) for i in range(n_req)]
+    plist = [params(max_tokens=3 + (i % 3) * 3) for i in range(n_req)]  # a third of them ends after 3 tokens, a third after 6
+    top = 128 if n_req <= 128 else 256
+    eng = engine(model, num_blocks=800, block_size=16, record_logits=True, max_admit=256, max_running=top)
+    assert top in eng.graphs.buckets and 2 * top not in eng.graphs.buckets, "captured when the engine is built, up to max_running"
     reqs = [eng.add(p, s) for p, s in zip(prompts, plist)]
     sizes = []
     while eng.sched.has_work:
         eng.step()
         sizes.append(len(eng.sched.running))
-    assert max(sizes) == 100 and eng.graphs.replays >= 7
-    check_teacher_forced(reqs, prompts, cfg, w, dt, f"bucket of 128 {dtype}")
+    assert max(sizes) == n_req and eng.graphs.replays >= 7
+    check_teacher_forced(reqs, prompts, cfg, w, dt, f"bucket of {top} {dtype}")
     eng.cache.check()
     assert eng.cache.live == []
 
