@@ -11,7 +11,8 @@
 // Also returned: the token's log-probability under the raw logits at temperature 1, and under
 // the processed distribution it was drawn from (0 for greedy rows).
 // Tie rule for the nucleus: tokens with equal logits are kept or dropped together by top-p;
-// at the top-k boundary equal logits are taken in order of their index.
+// at the top-k boundary equal logits are taken in order of their index.  The two thresholds are found without a
+// sort, a byte of the ordering key at a time (radix_threshold: four passes over the row each).
 #include "common.cuh"
 
 namespace {
@@ -28,32 +29,155 @@ struct RowArgs {
     int vocab;
 };
 
-// sum over the row of exp(z / temp - max_s) for the tokens whose ordering key exceeds tau
-__device__ float block_sum_if_key_gt(const RowArgs& r, float temp, float max_s, unsigned tau, float* scratch) {
-    float s = 0.f;
-    for (int i = threadIdx.x; i < r.vocab; i += kThreads) {
-        const float v = r.z[i] / temp;
-        if (order_key(v) > tau) s += expf(v - max_s);
-    }
-    return ns_block_sum(s, scratch);
+// The smallest key t such that measure(keys > t) <= target - the lowest key that is still kept - without a sort.
+// The measure is a count (top-k) or the mass exp(v - max_s) in fixed point (top-p: steps of 2^-40, so that sums do not
+// depend on the order of the atomics); for the mass the target is `fraction` of the row's total.
+//   pass 1  every value goes into one of 256 bins of an eighth of a nat below the row's maximum (each warp into bins
+//           of its own in shared memory, added in a fixed order afterwards; what lies 32 nats or more below goes to
+//           the last bin through registers).  A scan from the top finds the bin that holds the threshold.
+//   pass 2  the keys of that bin are collected in shared memory,
+//   then    the threshold is found among them a byte of the key at a time (four rounds over the list).
+// If the bin is the last one or holds more keys than the list, the bytes are found by passes over the row instead.
+// *above = measure(keys > t).
+constexpr int kBins = 256;
+constexpr float kMassOneF = 1099511627776.f;  // 2^40
+constexpr int kListCap = (kThreads / 32) * kBins * 2;  // u32 keys in the space of the warps' bins
+
+__device__ __forceinline__ float key_value(unsigned key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+__device__ __forceinline__ int value_bin(float v, float max_s) {
+    const float d = (max_s - v) * 8.f;
+    return d < 255.f ? (int)d : 255;  // (also what is not a number or infinitely far)
+}
+__device__ __forceinline__ unsigned long long measure_of(float v, float max_s, bool by_mass) {
+    return by_mass ? (unsigned long long)(expf(v - max_s) * kMassOneF) : 1ull;
 }
 
-__device__ int block_count_key_gt(const RowArgs& r, float temp, unsigned tau, int* iscratch) {
-    int c = 0;
-    for (int i = threadIdx.x; i < r.vocab; i += kThreads)
-        if (order_key(r.z[i] / temp) > tau) ++c;
-    // integer block sum
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+// f(value) for every logit of the row, 16 bytes per load where the row allows it: a pass is bound by the latency of its
+// loads (one block, 126 values per thread), so fewer and wider loads make it shorter.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const RowArgs& r, F f) {
+    const int tid = threadIdx.x;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(r.z) & 15u) == 0) {
+        const int n4 = r.vocab >> 2;
+        const float4* z4 = reinterpret_cast<const float4*>(r.z);
+#pragma unroll 2
+        for (int i = tid; i < n4; i += kThreads) {
+            const float4 x = __ldg(z4 + i);
+            f(x.x), f(x.y), f(x.z), f(x.w);
+        }
+        done = n4 << 2;
+    }
+    for (int i = done + tid; i < r.vocab; i += kThreads) f(r.z[i]);
+}
+
+// One byte of the descent over the counts in tot[]: the lowest byte d with run + (bins above d) <= target.
+__device__ __forceinline__ int lowest_byte(const unsigned long long* tot, unsigned long long target, unsigned long long* run) {
+    int d = kBins - 1;
+    while (d > 0 && *run + tot[d] <= target) { *run += tot[d]; --d; }
+    return d;
+}
+
+__device__ unsigned radix_threshold(const RowArgs& r, float temp, float max_s, bool by_mass, double fraction,
+                                    unsigned long long count_target, unsigned long long* hist, unsigned long long* tot,
+                                    unsigned long long* sh, unsigned long long* above) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // ---- pass 1: bins by value ----
+    for (int i = tid; i < (kThreads / 32) * kBins; i += kThreads) hist[i] = 0ull;
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) iscratch[threadIdx.x >> 5] = c;
+    unsigned long long* mine = hist + warp * kBins;
+    unsigned long long far = 0ull;
+    for_each_logit(r, [&](float zi) {
+        const float v = zi / temp;
+        const int b = value_bin(v, max_s);
+        const unsigned long long w = measure_of(v, max_s, by_mass);
+        if (b == kBins - 1) far += w;
+        else atomicAdd(mine + b, w);
+    });
+    for (int o = 16; o > 0; o >>= 1) far += __shfl_xor_sync(0xffffffffu, far, o);
+    if (lane == 0) mine[kBins - 1] = far;
     __syncthreads();
-    int t = (threadIdx.x < kThreads / 32) ? iscratch[threadIdx.x] : 0;
-    if (threadIdx.x < 32) {
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (threadIdx.x == 0) iscratch[0] = t;
+    if (tid < kBins) {
+        unsigned long long t = 0ull;
+        for (int w = 0; w < kThreads / 32; ++w) t += hist[w * kBins + tid];
+        tot[tid] = t;
     }
     __syncthreads();
-    return iscratch[0];
+    if (tid == 0) {
+        unsigned long long total = 0ull;
+        for (int b = 0; b < kBins; ++b) total += tot[b];
+        const unsigned long long target = by_mass ? (unsigned long long)((double)total * fraction) : count_target;
+        // bins run from the highest values down: the threshold lies in the last bin d whose higher bins fit the target
+        unsigned long long run = 0ull;
+        int d = 0;
+        while (d < kBins - 1 && run + tot[d] <= target) { run += tot[d]; ++d; }
+        sh[0] = run, sh[1] = (unsigned long long)d, sh[2] = target;
+        sh[3] = (d == kBins - 1 && run + tot[d] <= target) ? 1ull : 0ull;  // everything fits: every key is kept
+        sh[4] = total;
+    }
+    __syncthreads();
+    unsigned long long run_above = sh[0];
+    const int bin = (int)sh[1];
+    const unsigned long long target = sh[2];
+    if (sh[3]) {
+        *above = sh[4];
+        __syncthreads();
+        return 0u;
+    }
+    __syncthreads();
+    // ---- pass 2: the keys of that bin, into the space of the warps' bins ----
+    unsigned* list = reinterpret_cast<unsigned*>(hist);
+    unsigned* n_list = reinterpret_cast<unsigned*>(sh + 5);
+    bool listed = bin < kBins - 1;
+    if (listed) {
+        if (tid == 0) *n_list = 0u;
+        __syncthreads();
+        for_each_logit(r, [&](float zi) {
+            const float v = zi / temp;
+            if (value_bin(v, max_s) == bin) {
+                const unsigned at = atomicAdd(n_list, 1u);
+                if (at < (unsigned)kListCap) list[at] = order_key(v);
+            }
+        });
+        __syncthreads();
+        listed = *n_list <= (unsigned)kListCap;
+    }
+    const int n = listed ? (int)*n_list : 0;
+    // ---- the threshold's four bytes: over the list, or over the row's values of that bin ----
+    unsigned prefix = 0u;
+    for (int level = 0; level < 4; ++level) {
+        const int shift = 24 - 8 * level;
+        if (tid < kBins) tot[tid] = 0ull;
+        __syncthreads();
+        if (listed) {
+            for (int i = tid; i < n; i += kThreads) {
+                const unsigned key = list[i];
+                if (level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)))
+                    atomicAdd(tot + ((key >> shift) & 255u), measure_of(key_value(key), max_s, by_mass));
+            }
+        } else {
+            for_each_logit(r, [&](float zi) {
+                const float v = zi / temp;
+                const unsigned key = order_key(v);
+                if (value_bin(v, max_s) == bin && (level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8))))
+                    atomicAdd(tot + ((key >> shift) & 255u), measure_of(v, max_s, by_mass));
+            });
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long run = run_above;
+            sh[1] = (unsigned long long)lowest_byte(tot, target, &run);
+            sh[0] = run;
+        }
+        __syncthreads();
+        run_above = sh[0];
+        prefix |= (unsigned)sh[1] << shift;
+        __syncthreads();
+    }
+    *above = run_above;
+    return prefix;
 }
 
 constexpr int kChunks = 16;        // blocks that share one row in the first pass
@@ -118,12 +242,14 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     __shared__ float fscratch[32];
-    __shared__ int iscratch[32];
     __shared__ float seg_prefix[kThreads];
     __shared__ int seg_eq_prefix[kThreads];
     __shared__ int found, last_kept;
     __shared__ float smax[32];
     __shared__ int sidx[32];
+    __shared__ unsigned long long bin_total[kBins];
+    __shared__ unsigned long long descent[6];
+    extern __shared__ unsigned long long warp_bins[];  // [warps][kBins]
 
     const int row = blockIdx.x;
     const float* z = logits + (size_t)row * ld;
@@ -173,37 +299,22 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     unsigned tau = 0u;       // every finite logit has key > 0
     int n_eq = 0x7fffffff;   // all tokens equal to tau
     if (nucleus) {
-        // softmax denominator over the whole row (the reference sorts, then takes softmax of all)
-        float s = 0.f;
-        for (int i = tid; i < vocab; i += kThreads) s += expf(z[i] / temp - max_s);
-        const float denom = ns_block_sum(s, fscratch);
-
         unsigned tau_p = 0u;
         if (p_keep < 1.f) {
-            // smallest key t with mass(key > t) <= top_p; kept by top-p = {key >= t}.  Logits that tie exactly at t are
-            // all kept: the reference's descending sort (spec/sampling.py:29-33) keeps whichever of them it happens to
-            // place first, which no order of the vocabulary decides
-            unsigned lo = 0u;  // bitwise descent: build the smallest t for which the predicate holds
-            for (int bit = 31; bit >= 0; --bit) {
-                // candidate with this bit cleared and all lower bits set is the largest value in the lower half
-                const unsigned cand = lo | ((1u << bit) - 1u);
-                const float mass = block_sum_if_key_gt(r, temp, max_s, cand, fscratch) / denom;
-                if (!(mass <= p_keep)) lo |= (1u << bit);  // predicate false on the lower half's top: answer is above
-            }
-            tau_p = lo;  // kept = {key >= tau_p} = {key > tau_p - 1}
+            // smallest key t with mass(key > t) <= top_p of the row's softmax mass (the reference sorts, takes the softmax of
+            // all and keeps a token while the mass before it is <= top_p, spec/sampling.py:29-33); kept by top-p =
+            // {key >= t}.  Logits that tie exactly at t are all kept: the reference's descending sort keeps whichever of them
+            // it happens to place first, which no order of the vocabulary decides
+            unsigned long long above;
+            tau_p = radix_threshold(r, temp, max_s, true, (double)fmaxf(p_keep, 0.f), 0ull, warp_bins, bin_total, descent, &above);
         }
         unsigned tau_k = 0u;
         int eq_k = 0x7fffffff;
         if (k > 0 && k < vocab) {
-            // k-th largest key: smallest t with count(key > t) <= k - 1
-            unsigned lo = 0u;
-            for (int bit = 31; bit >= 0; --bit) {
-                const unsigned cand = lo | ((1u << bit) - 1u);
-                const int cnt = block_count_key_gt(r, temp, cand, iscratch);
-                if (!(cnt <= k - 1)) lo |= (1u << bit);
-            }
-            tau_k = lo;
-            eq_k = k - block_count_key_gt(r, temp, tau_k, iscratch);
+            // k-th largest key: smallest t with count(key > t) <= k - 1; the tokens equal to it fill the k places that are left
+            unsigned long long above;
+            tau_k = radix_threshold(r, temp, max_s, false, 0.0, (unsigned long long)(k - 1), warp_bins, bin_total, descent, &above);
+            eq_k = k - (int)above;
         }
         // combine: both kept sets are prefixes of the descending order; take the shorter one
         if (k > 0 && k < vocab && tau_k >= tau_p) {
@@ -336,7 +447,13 @@ NS_API int ns_sample_rows(const float* logits, long long ld, int n_rows, int voc
     if (vocab <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_sample_rows: vocab=%d", vocab);
     if (!partial) NS_FAIL(NS_ERR_ARGUMENT, "ns_sample_rows: no scratch for the first pass");
     NS_LAUNCH((sample_partial_kernel), dim3(n_rows, kChunks), kPartialThreads, 0, stream, logits, ld, vocab, partial);
-    NS_LAUNCH((sample_rows_kernel), n_rows, kThreads, 0, stream, logits, ld, vocab, temperature, top_k, top_p, u,
+    constexpr int kBinBytes = (kThreads / 32) * kBins * (int)sizeof(unsigned long long);
+    static bool configured = false;
+    if (!configured) {
+        NS_CUDA(cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBinBytes));
+        configured = true;
+    }
+    NS_LAUNCH((sample_rows_kernel), n_rows, kThreads, kBinBytes, stream, logits, ld, vocab, temperature, top_k, top_p, u,
               (const float*)partial, token, logprob_raw, logprob_proc);
     NS_CHECK_LAUNCH("ns_sample_rows");
     return NS_OK;
