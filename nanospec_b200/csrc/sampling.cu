@@ -362,29 +362,25 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
         return false;
     };
 
-    // kept log-sum-exp
-    float ks = 0.f;
-    {
-        int eq_seen = 0;
-        for (int i = s0; i < s1; ++i) {
-            const float v = z[i] / temp;
-            if (kept(i, v, eq_seen)) ks += expf(v - max_s);
-        }
-    }
-    const float lse_s = logf(ns_block_sum(ks, fscratch)) + max_s;
-
-    // segment sums of probabilities, exclusive prefix in thread order
+    // One pass for the kept tokens' weights exp(v - max_s): their sum per segment (exclusive prefix in thread order below)
+    // and each thread's last kept token.  The draw compares running sums of the same weights with u x their total, so
+    // the normalised probabilities are never formed.
     float segsum = 0.f;
+    int last = -1;
     {
         int eq_seen = 0;
         for (int i = s0; i < s1; ++i) {
             const float v = z[i] / temp;
-            if (kept(i, v, eq_seen)) segsum += expf(v - lse_s);
+            if (kept(i, v, eq_seen)) {
+                segsum += expf(v - max_s);
+                last = i;
+            }
         }
     }
     seg_prefix[tid] = segsum;
     if (tid == 0) { found = 0x7fffffff; last_kept = 0; }
     __syncthreads();
+    if (last >= 0) atomicMax(&last_kept, last);  // used only if no thread's sum passes the target
     if (warp == 0) {
         // 32 consecutive segments per lane, then a warp scan of the lane totals
         float local = 0.f;
@@ -404,21 +400,25 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int vocab, co
     }
     __syncthreads();
     const float total = fscratch[0];
+    const float lse_s = logf(total) + max_s;
     const float target = u[row] * total;
     {
-        // the running sum is compared with the target only right after a kept token has been added: a token
-        // outside the set can never be reported, whatever the rounding of the scanned prefix
-        float run = seg_prefix[tid];
-        int eq_seen = 0, last = -1;
-        for (int i = s0; i < s1; ++i) {
-            const float v = z[i] / temp;
-            if (kept(i, v, eq_seen)) {
-                run += expf(v - lse_s);
-                last = i;
-                if (run > target) { atomicMin(&found, i); break; }
+        // The running sum is compared with the target only right after a kept token has been added: a token outside
+        // the set can never be reported, whatever the rounding of the scanned prefix.  A segment whose sum ends clearly
+        // below the target cannot hold the crossing and is not walked again; one that starts above it reports its
+        // first kept token at once (the smallest index reported wins).
+        const float begin = seg_prefix[tid];
+        if (segsum > 0.f && !(begin + segsum < target - 1e-4f * total)) {
+            float run = begin;
+            int eq_seen = 0;
+            for (int i = s0; i < s1; ++i) {
+                const float v = z[i] / temp;
+                if (kept(i, v, eq_seen)) {
+                    run += expf(v - max_s);
+                    if (run > target) { atomicMin(&found, i); break; }
+                }
             }
         }
-        if (last >= 0) atomicMax(&last_kept, last);  // used only if no thread's sum passed the target
     }
     __syncthreads();
     if (tid == 0) {
